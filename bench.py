@@ -1,20 +1,24 @@
 """Benchmark of the MX-GEMM hot path: `python bench.py --gpus N --steps K --warmup W [--impl reference]`.
 
-Workload (N=1): BASELINE configuration 2 -- M=N=K=8192, per-tensor scales (bf16 [1,1]), fused
-output quantisation to e4m3 in [1,16] groups with bf16 scales. One step = one call of the operator on
-one batch of synthetic operands resident in HBM. With N>1 every rank runs the same per-GPU problem on
-its own N-slice of a weight that is N times wider (weak scaling, no data-path collective): the global
-problem is M=8192, N=8192*N, K=8192.
+Workload: BASELINE configuration 2 -- M=N=K=8192, per-tensor scales (bf16 [1,1]), fused output
+quantisation to e4m3 in [1,16] groups with bf16 scales. One step = one call of the operator on one
+batch of synthetic operands resident in HBM. With N>1 the SAME problem is sharded along N (strong
+scaling): every rank holds `left` and the rows [r*8192/N, (r+1)*8192/N) of the physical [N, K]
+weight and computes its column block of the result; the GEMM needs no collective. `value` is the
+whole job's TFLOP/s: 2*M*N*K divided by the slowest rank's time per step.
 
-Prints ONE JSON line (rank 0): whole-job TFLOP/s, the tensor-core roofline of the kernel, the CPU
-baseline (the reference's torch dequantise-and-matmul path on the host cores) and the end-to-end
-number through the host-memory C-ABI entry point (copies inside the timed region).
+Prints ONE JSON line (rank 0): whole-job TFLOP/s, the tensor-core roofline of the kernel (burst, and
+a second figure from at least a second of back-to-back calls), the CPU baseline (the reference's torch
+dequantise-and-matmul path on the host cores), the end-to-end number through the host-memory C-ABI
+entry point (copies inside the timed region), and for N>1 the time with the full result gathered on
+every rank (NCCL all-gather / peer push) plus a parity check of the sharded path against the oracle.
 """
 
 from __future__ import annotations
 
 import argparse
 import ctypes
+import importlib.util
 import json
 import os
 import subprocess
@@ -29,21 +33,24 @@ ROOT = Path(__file__).resolve().parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
-M = N_LOCAL = K = 8192
+M = N = K = 8192
 QN = 16
 METRIC = "FP8 MX-GEMM TFLOP/s & % of B200 FP8 peak (HBM GB/s for small M)"
 WORKLOAD = "c2: M=N=K=8192 per-tensor scales, fused [1,16] e4m3 output quantisation with bf16 scales"
-FLOPS_PER_STEP = 2.0 * M * N_LOCAL * K
-# compulsory bytes of one step: left + right + e4m3 out + bf16 group scales + two bf16 input scales
-ALGO_BYTES = M * K + N_LOCAL * K + M * N_LOCAL + M * (N_LOCAL // QN) * 2 + 4
+FLOPS_TOTAL = 2.0 * M * N * K
 NOMINAL_FP8_TFLOPS = 4500.0
 
 
+def algo_bytes(n_local: int) -> int:
+    """Compulsory bytes of one rank's step: left + its rows of right + e4m3 out + bf16 group scales + two scales."""
+    return M * K + n_local * K + M * n_local + M * (n_local // QN) * 2 + 4
+
+
 def make_operands(seed: int):
-    """Seeded synthetic operands of the c2 shape, generated on the CPU (pinned)."""
+    """Seeded synthetic operands of the c2 shape, generated on the CPU."""
     g = torch.Generator().manual_seed(seed)
     left = torch.randn(M, K, generator=g, dtype=torch.bfloat16).to(torch.float8_e4m3fn)
-    right_phys = torch.randn(N_LOCAL, K, generator=g, dtype=torch.bfloat16).to(torch.float8_e4m3fn)
+    right_phys = torch.randn(N, K, generator=g, dtype=torch.bfloat16).to(torch.float8_e4m3fn)
     ls = (0.5 + 1.5 * torch.rand(1, 1, generator=g)).to(torch.bfloat16)
     rs = (0.5 + 1.5 * torch.rand(1, 1, generator=g)).to(torch.bfloat16)
     return left, right_phys, ls, rs
@@ -59,84 +66,168 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """SM clock and throttle reasons of one GPU while a timed region runs: NVML polled from a thread every
+    `period` seconds (reads only), nvidia-smi at its fastest loop rate if NVML is not importable."""
 
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
-    def __init__(self, index: int):
-        self.index = index
+    def __init__(self, device_index: int, period: float = 0.002):
+        self.device_index = device_index
+        self.period = period
+        self.sm, self.max_sm, self.reasons = [], None, set()
+        self.stop = threading.Event()
+        self.thread = None
         self.proc = None
-        self.lines = []
+        self.source = None
+
+    def _nvml_handle(self):
+        import pynvml
+
+        pynvml.nvmlInit()
+        uuid = "GPU-" + str(torch.cuda.get_device_properties(self.device_index).uuid)
+        return pynvml, pynvml.nvmlDeviceGetHandleByUUID(uuid.encode() if hasattr(uuid, "encode") else uuid)
+
+    def _poll_nvml(self, nv, h):
+        get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            nv.nvmlDeviceGetCurrentClocksThrottleReasons
+        while not self.stop.is_set():
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+                bits = int(get_reasons(h))
+                for bit, name in self.REASONS.items():
+                    if bits & bit:
+                        self.reasons.add(name)
+            except Exception:
+                break
+            self.stop.wait(self.period)
+
+    def _poll_smi(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                self.sm.append(float(parts[0]))
+                self.max_sm = max(self.max_sm or 0.0, float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"], parts[2:6]):
+                if val.lower().startswith("active"):
+                    self.reasons.add(name)
 
     def __enter__(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
-                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._pump, daemon=True)
+            nv, h = self._nvml_handle()
+            self.max_sm = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._poll_nvml, args=(nv, h), daemon=True)
+            self.source = f"nvml every {self.period * 1e3:.0f} ms"
+        except Exception:
+            query = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+                     "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+            try:
+                self.proc = subprocess.Popen(
+                    ["nvidia-smi", f"--query-gpu={query}", "--format=csv,noheader,nounits", "-lms", "10", "-i",
+                     str(self.device_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                self.thread = threading.Thread(target=self._poll_smi, daemon=True)
+                self.source = "nvidia-smi -lms 10"
+            except OSError:
+                self.thread = None
+        if self.thread is not None:
             self.thread.start()
-        except OSError:
-            self.proc = None
         return self
 
-    def _pump(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
-
     def __exit__(self, *exc):
+        self.stop.set()
         if self.proc is not None:
-            time.sleep(0.15)
+            time.sleep(0.05)
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
             except subprocess.TimeoutExpired:
                 self.proc.kill()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
         return False
 
     def summary(self):
-        sm, mx, reasons = [], 0.0, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 9:
-                continue
+        sm = sorted(self.sm)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_min_mhz": sm[0] if sm else None,
+                "sm_max_mhz": self.max_sm, "reasons": sorted(self.reasons), "samples": len(sm), "source": self.source}
+
+
+def bind_to_gpu_numa_node(device_index: int):
+    """Run this process on the CPUs next to its GPU, so that the pinned host buffers it allocates (first touch)
+    and the threads that drive the copies are local to the GPU's PCIe root. Best effort; returns the CPU list."""
+    try:
+        p = torch.cuda.get_device_properties(device_index)
+        addr = f"{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+        text = Path(f"/sys/bus/pci/devices/{addr}/local_cpulist").read_text().strip()
+        cpus = set()
+        for part in text.split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+            return text
+    except Exception:
+        pass
+    return None
+
+
+# -------------------------------------------------------------------------------------------------
+# CPU legs: the reference's torch path on the host cores
+# -------------------------------------------------------------------------------------------------
+def reference_utils():
+    """The reference's own mxblas/utils.py, loaded from its source tree when that is present next to this
+    repository (or at MXBLAS_REFERENCE_DIR); None where it is not (the GPU boxes)."""
+    for root in (os.environ.get("MXBLAS_REFERENCE_DIR"), str(ROOT.parent / "reference")):
+        if root and (Path(root) / "mxblas" / "utils.py").exists():
             try:
-                sm.append(float(parts[1]))
-                mx = max(mx, float(parts[2]))
-            except ValueError:
+                spec = importlib.util.spec_from_file_location("_reference_mxblas_utils", Path(root) / "mxblas" / "utils.py")
+                mod = importlib.util.module_from_spec(spec)
+                spec.loader.exec_module(mod)
+                return mod
+            except Exception:
                 continue
-            for name, val in zip(names, parts[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+    return None
 
 
-# -------------------------------------------------------------------------------------------------
-# CPU baseline: the reference's torch path (oracle restatement) on the host cores
-# -------------------------------------------------------------------------------------------------
-def cpu_baseline(left, right_phys, ls, rs, rows: int, budget_s: float, min_iters: int = 1):
-    """Time dequantise + fp32 matmul + group quantisation on the first `rows` rows of left."""
+def cpu_path(kind_pref: str = "auto"):
+    """(callable(left_rows, right_phys, ls, rs), kind, description) of the CPU implementation to time."""
+    ref = reference_utils() if kind_pref != "port" else None
+    if ref is not None:
+        def run(sub, right_phys, ls, rs):
+            a32 = ref.block_dequant(sub, ls.float(), (sub.shape[0], K), torch.float32)
+            b32 = ref.block_dequant(right_phys, rs.float(), (right_phys.shape[0], K), torch.float32)
+            c32 = torch.mm(a32, b32.t())
+            return ref.block_quant(c32, (1, QN))
+        return run, "reference", ("the reference's own mxblas.utils.block_dequant x2 + fp32 torch.mm + "
+                                  f"mxblas.utils.block_quant (1,{QN})")
     from oracle import mx_oracle as orc
 
+    def run(sub, right_phys, ls, rs):
+        return orc.mx_gemm(sub, right_phys.t(), ls, rs.t(), True, (1, QN))
+    return run, "port", f"oracle port of the reference's path: block_dequant x2 + fp32 torch.mm + [1,{QN}] group quantisation"
+
+
+def cpu_baseline(left, right_phys, ls, rs, rows: int, budget_s: float, min_iters: int = 1):
+    """Time dequantise + fp32 matmul + group quantisation on the first `rows` rows of left."""
+    run, kind, what = cpu_path()
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
     sub = left[:rows]
-    flops = 2.0 * rows * N_LOCAL * K
+    flops = 2.0 * rows * N * K
     times = []
     t_end = time.perf_counter() + budget_s
     while len(times) < min_iters or (time.perf_counter() < t_end and len(times) < 50):
         t0 = time.perf_counter()
-        orc.mx_gemm(sub, right_phys.t(), ls, rs.t(), True, (1, QN))
+        run(sub, right_phys, ls, rs)
         times.append(time.perf_counter() - t0)
     times.sort()
     med = times[len(times) // 2]
-    return {"value": flops / med / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
-            "sample": f"first {rows} of {M} rows of left, full N and K (block_dequant x2 + fp32 torch.mm + "
-                      f"[1,{QN}] group quantisation), median of {len(times)} runs",
+    return {"value": flops / med / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": kind,
+            "sample": f"first {rows} of {M} rows of left, full N and K ({what}), median of {len(times)} runs",
             "seconds_per_sample": med}
 
 
@@ -151,14 +242,14 @@ def run_reference_arm(args, rank: int):
     t0 = time.perf_counter()
     res = [cpu_baseline(left, right_phys, ls, rs, rows, 0.0, 1) for _ in range(args.steps)]
     total = time.perf_counter() - t0
-    val = 2.0 * rows * N_LOCAL * K * args.steps / total / 1e12
+    val = 2.0 * rows * N * K * args.steps / total / 1e12
     cb = dict(res[0])
     cb["value"] = val
-    cb["sample"] = f"each step = first {rows} of {M} rows of left, full N and K; {args.steps} steps"
+    cb["sample"] = f"each step = first {rows} of {M} rows of left, full N and K; {args.steps} steps; " + cb["sample"]
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / args.steps * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 (CPU) for e4m3 operands",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32 (CPU) for e4m3 operands",
         "data": "synthetic", "config": {"workload": WORKLOAD, "note": "reference CPU path: torch dequantise-and-"
                                         "matmul + group quantisation on host cores; the reference's GPU kernels "
                                         "are sm_90a-only and cannot run on B200"},
@@ -168,6 +259,33 @@ def run_reference_arm(args, rank: int):
 
 
 # -------------------------------------------------------------------------------------------------
+def dist_parity(dist, dev, rank: int, world: int) -> bool:
+    """One small problem through the N-sharded path with the full result gathered (NCCL, and peer push),
+    checked on every rank against the CPU oracle (the checker, not the thing measured)."""
+    from mxblas_b200.dist import sharded_mx_gemm
+    from oracle import mx_oracle as orc
+
+    m, n, k = 512, 2048, 512
+    g = torch.Generator().manual_seed(1234)
+    left = torch.randn(m, k, generator=g).to(torch.float8_e4m3fn)
+    right_phys = torch.randn(n, k, generator=g).to(torch.float8_e4m3fn)
+    ls = (0.5 + 1.5 * torch.rand(1, 1, generator=g)).to(torch.bfloat16)
+    rs = (0.5 + 1.5 * torch.rand(1, 1, generator=g)).to(torch.bfloat16)
+    dargs = (left.to(dev), right_phys.to(dev).t(), ls.to(dev), rs.to(dev).t(), True, torch.Size((1, QN)))
+    c32 = orc.mx_gemm_c32(left, right_phys.t(), ls, rs.t())
+    codes, scales, _ = orc.quantize_groups(c32, QN, torch.bfloat16)
+    ok = True
+    for mode in (True, "peer"):
+        out, osc = sharded_mx_gemm(*dargs, gather=mode)
+        torch.cuda.synchronize()
+        d = orc.fp8_code_distance(out.cpu(), codes)
+        ok = ok and tuple(out.shape) == (m, n) and float((d == 0).float().mean()) >= 0.999 and int(d.max()) <= 1
+        ok = ok and int(orc.ulp_distance(osc.cpu().contiguous(), scales).max()) <= 1
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    return bool(flag.item())
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -176,6 +294,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-sustained", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -189,81 +308,145 @@ def main():
 
     import torch.distributed as dist
 
-    import mxblas_b200 as mxblas
-    from mxblas_b200 import _ext
-    from mxblas_b200.mx_gemm import get_meta_info, make_problem
-
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    all_cpus = os.sched_getaffinity(0)
+    numa_cpus = bind_to_gpu_numa_node(local_rank)
+
+    import mxblas_b200 as mxblas
+    from mxblas_b200 import _ext
+    from mxblas_b200.dist import shard_bounds, sharded_mx_gemm
+    from mxblas_b200.mx_gemm import get_meta_info, make_problem
+
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
     mxblas.register_all_kernels()
-    left, right_phys, ls, rs = make_operands(rank)
-    ld, rd, lsd, rsd = left.to(dev), right_phys.to(dev), ls.to(dev), rs.to(dev)
+    n0, n1 = shard_bounds(N, world, rank, sn=N, qn=QN)
+    n_local = n1 - n0
+    left, right_phys, ls, rs = make_operands(0)  # the same full problem on every rank
+    right_local = right_phys[n0:n1].contiguous()
+    ld, rd, lsd, rsd = left.to(dev), right_local.to(dev), ls.to(dev), rs.to(dev)
     qsize = torch.Size((1, QN))
 
     def step():
-        return mxblas.mx_gemm_kernel(ld, rd.t(), lsd, rsd.t(), True, qsize)
+        # this rank's column block of the result through the N-sharded operator (no collective)
+        return sharded_mx_gemm(ld, rd.t(), lsd, rsd.t(), True, qsize, right_is_local=True)
 
     def sync_all():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    parity = dist_parity(dist, dev, rank, world) if world > 1 else None
+
     for _ in range(args.warmup):
         step()
     sync_all()
 
+    # Timing rule: a step's inputs must not sit in L2 from the step before. One rank's share of the problem is
+    # 200 MiB at N=1 (larger than the 126 MB L2, streamed anew every step) but 81 MiB at N=8, so for N>1 each
+    # step is timed by its own event pair and a 256 MiB buffer is read between the steps (outside the pairs).
+    flush_between = algo_bytes(n_local) < 2 * 126e6
+    flush_buf = torch.zeros(256 << 20, dtype=torch.uint8, device=dev) if flush_between else None
+
+    def timed(fn, steps):
+        sync_all()
+        if not flush_between:
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(steps):
+                fn()
+            end.record()
+            sync_all()
+            total = start.elapsed_time(end)
+        else:
+            pairs = []
+            for _ in range(steps):
+                flush_buf.view(torch.int32).sum()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                pairs.append((e0, e1))
+            sync_all()
+            total = sum(a.elapsed_time(b) for a, b in pairs)
+        t = torch.tensor([total], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     # ---- device-resident timing: K steps between two events on the launching stream --------------
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = _ext.launch_count()
     with ClockSampler(local_rank) as clocks:
-        sync_all()
-        start.record()
-        for _ in range(args.steps):
-            step()
-        end.record()
-        sync_all()
+        elapsed_ms = timed(step, args.steps)
     launches = _ext.launch_count() - launches0
-    elapsed_ms = torch.tensor([start.elapsed_time(end)], device=dev)
-    if world > 1:
-        dist.all_reduce(elapsed_ms, op=dist.ReduceOp.MAX)
-    elapsed_ms = float(elapsed_ms.item())
     status = _ext.device_status()
     ms_per_step = elapsed_ms / args.steps
-    value = FLOPS_PER_STEP * world / (ms_per_step * 1e-3) / 1e12
+    value = FLOPS_TOTAL / (ms_per_step * 1e-3) / 1e12
 
     # ---- roofline of the dominant (only) kernel: per-launch duration from the same events --------
     peaks = measured_peaks()
-    sustained = elapsed_ms > 1000.0
-    fp8_peak = 2.0 * (peaks["bf16_sustained"] if sustained else peaks["bf16_burst"])
-    achieved = FLOPS_PER_STEP / (ms_per_step * 1e-3) / 1e12
+    flops_launch = 2.0 * M * n_local * K
+    burst = elapsed_ms <= 1000.0
+    fp8_peak = 2.0 * (peaks["bf16_burst"] if burst else peaks["bf16_sustained"])
+    achieved = flops_launch / (ms_per_step * 1e-3) / 1e12
+    of = "of measured" if peaks["source"] == "measured" else "of fallback"
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak,
         "traffic": None,
-        "peak_note": f"2 x {peaks['source']} dense bf16 cuBLAS {'sustained' if sustained else 'burst'} TFLOP/s "
-                     "(FP8 runs at twice the bf16 tensor rate); of measured" if peaks["source"] == "measured"
-                     else "2 x fallback bf16 figure; of fallback",
+        "peak_note": f"2 x {peaks['source']} dense bf16 cuBLAS {'burst' if burst else 'sustained'} TFLOP/s "
+                     f"(FP8 runs at twice the bf16 tensor rate); {of}",
         "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,
-        "algorithmic_bytes": ALGO_BYTES, "hbm_gbs": ALGO_BYTES / (ms_per_step * 1e-3) / 1e9,
-        "kernel": "mx_gemm_sm100 (one launch per step)",
+        "algorithmic_flops_per_launch": flops_launch,
+        "algorithmic_bytes": algo_bytes(n_local), "hbm_gbs": algo_bytes(n_local) / (ms_per_step * 1e-3) / 1e9,
+        "kernel": "mx_gemm_sm100_pair<PairCfg<256, SCALE_EPILOGUE, OUT_QUANT_Y, 8>> (one launch per step)",
     }
     traffic_file = ROOT / "profiles" / "traffic_c2.json"
-    if traffic_file.exists():
+    if traffic_file.exists() and world == 1:
         roofline["traffic"] = json.loads(traffic_file.read_text()).get("dram_bytes_per_launch")
+
+    # ---- the same kernel over at least a second of back-to-back calls, clocks sampled throughout --
+    if not args.no_sustained:
+        n_long = max(args.steps, int(1200.0 / ms_per_step) + 1)
+        with ClockSampler(local_rank, period=0.01) as long_clocks:
+            long_ms = timed(step, n_long)
+        long_tf = flops_launch / (long_ms / n_long * 1e-3) / 1e12
+        roofline["sustained"] = {
+            "achieved": long_tf, "peak": 2.0 * peaks["bf16_sustained"], "unit": "TFLOP/s",
+            "frac": long_tf / (2.0 * peaks["bf16_sustained"]), "frac_of_nominal_4500": long_tf / NOMINAL_FP8_TFLOPS,
+            "calls": n_long, "seconds": long_ms * 1e-3, "ms_per_step": long_ms / n_long,
+            "clocks": long_clocks.summary(), "peak_note": f"2 x {peaks['source']} sustained bf16 cuBLAS TFLOP/s; {of}"}
+
+    # ---- N > 1: the same step with the full result on every rank ----------------------------------
+    gathered = None
+    if world > 1:
+        g_steps = max(3, min(args.steps, 10))
+
+        def step_nccl():
+            return sharded_mx_gemm(ld, rd.t(), lsd, rsd.t(), True, qsize, right_is_local=True, gather=True)
+
+        def step_peer():
+            return sharded_mx_gemm(ld, rd.t(), lsd, rsd.t(), True, qsize, right_is_local=True, gather="peer")
+
+        for fn in (step_nccl, step_peer):
+            for _ in range(3):
+                fn()
+        gathered = {"nccl_all_gather_ms_per_step": timed(step_nccl, g_steps) / g_steps,
+                    "peer_push_ms_per_step": timed(step_peer, g_steps) / g_steps, "steps": g_steps,
+                    "bytes_gathered_per_rank": (M * N + M * (N // QN) * 2) * (world - 1) // world}
 
     # ---- end to end through the host-memory C ABI: pinned host buffers, copies inside -------------
     e2e = None
     if not args.no_e2e:
-        hl, hr, hls, hrs = (t.pin_memory() for t in (left, right_phys, ls, rs))
-        hout = torch.empty(M, N_LOCAL, dtype=torch.float8_e4m3fn).pin_memory()
-        hsc = torch.empty(M, N_LOCAL // QN, dtype=torch.bfloat16).pin_memory()
+        hl, hr, hls, hrs = (t.pin_memory() for t in (left, right_local, ls, rs))
+        hout = torch.empty(M, n_local, dtype=torch.float8_e4m3fn).pin_memory()
+        hsc = torch.empty(M, n_local // QN, dtype=torch.bfloat16).pin_memory()
         e4, bf = torch.float8_e4m3fn, torch.bfloat16
-        meta = get_meta_info(e4, e4, bf, bf, True, (1, QN), None, (M, K), (K, N_LOCAL), (1, 1), (1, 1), (K, 1),
+        meta = get_meta_info(e4, e4, bf, bf, True, (1, QN), None, (M, K), (K, n_local), (1, 1), (1, 1), (K, 1),
                              (1, K), (1, 1), (1, 1), False, False)
-        problem = make_problem(meta, N_LOCAL, N_LOCAL // QN, False, False)
+        problem = make_problem(meta, n_local, n_local // QN, False, False)
 
         def host_step():
             st = _ext.lib.mxb_gemm_host(ctypes.byref(problem), hl.data_ptr(), hr.data_ptr(), hout.data_ptr(),
@@ -287,14 +470,17 @@ def main():
         # kernel: the fp32 sums may differ in the last bit, which moves a few codes per 10^6 across a rounding
         # boundary; the parity bar is >= 99.9 % identical codes
         same = float((hout.view(torch.uint8) == step()[0].cpu().view(torch.uint8)).float().mean())
-        e2e = {"value": FLOPS_PER_STEP * world / t_e2e / 1e12, "unit": "TFLOP/s",
-               "h2d_bytes_per_step": M * K + N_LOCAL * K + 4, "d2h_bytes_per_step": M * N_LOCAL + M * (N_LOCAL // QN) * 2,
+        e2e = {"value": FLOPS_TOTAL / t_e2e / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": M * K + n_local * K + 4, "d2h_bytes_per_step": M * n_local + M * (n_local // QN) * 2,
                "ms_per_step": t_e2e * 1e3, "steps": e2e_steps, "codes_identical_to_device_path": same,
-               "api": "mxb_gemm_host (C ABI, pinned host buffers, H2D + GEMM + D2H per call)"}
+               "host_buffers": "pinned" + (f", process bound to the GPU's local CPUs {numa_cpus}" if numa_cpus else ""),
+               "api": "mxb_gemm_host (C ABI, pinned host buffers, H2D + GEMM + D2H per call); per rank: all of left, "
+                      "its own rows of right, its own columns of the result"}
 
     # ---- CPU baseline (rank 0, N=1 only) ---------------------------------------------------------
     cb = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        os.sched_setaffinity(0, all_cpus)  # the CPU baseline gets every host core again
         cb = cpu_baseline(left, right_phys, ls, rs, rows=1024, budget_s=15.0, min_iters=3)
 
     if world > 1:
@@ -304,15 +490,22 @@ def main():
         return
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "e4m3 (fp32 accumulate)", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "global_shape": [M, N_LOCAL * world, K], "per_gpu_shape": [M, N_LOCAL, K],
-                   "sharding": f"N-sharded x{world}, no collective", "l2": "operands + outputs = 200 MiB per step, "
-                   "larger than the 126 MB L2 (no flush needed)"},
+        "config": {"workload": WORKLOAD, "global_shape": [M, N, K], "per_gpu_shape": [M, n_local, K],
+                   "sharding": f"N-sharded x{world} (each rank its own rows of the [N, K] weight), no collective",
+                   "l2": f"operands + outputs = {algo_bytes(n_local) / 2**20:.0f} MiB per step and rank: "
+                         + ("L2 flushed between the timed steps by a 256 MiB read, each step timed by its own pair of "
+                            "CUDA events (sum over the steps, max over ranks)" if flush_between else
+                            "larger than the 126 MB L2, back-to-back steps between one pair of CUDA events (no flush "
+                            "needed)")},
         "pct_of_nominal_fp8_peak": 100.0 * value / (NOMINAL_FP8_TFLOPS * world),
         "roofline": roofline, "cpu_baseline": cb, "e2e": e2e, "gpu_launches": int(launches),
         "clocks": clocks.summary(), "device_status": status,
     }
+    if world > 1:
+        line["gathered"] = gathered
+        line["dist_parity"] = parity
     print(json.dumps(line))
 
 

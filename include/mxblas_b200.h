@@ -154,6 +154,18 @@ int mxb_block_quant(const void* x, int x_dtype, long long m, long long k, long l
 int mxb_push_block(const void* src, long long src_pitch, void* const* dsts, int copies, long long dst_pitch,
                    long long rows, long long row_bytes, void* stream);
 
+/* mxb_push_block with a bound on the copy kernel's grid (blocks of 256 threads; 0 = no bound): a caller that
+ * runs the push beside a GEMM which leaves a few SMs free sizes it to those SMs (8 blocks each), so that no
+ * block of the push waits for, and then delays, the SMs of the GEMM. */
+int mxb_push_block_ex(const void* src, long long src_pitch, void* const* dsts, int copies, long long dst_pitch,
+                      long long rows, long long row_bytes, int max_blocks, void* stream);
+
+/* mxb_push_block on the copy engines (one 2-D device-to-device copy per destination): uses no SM, so it can
+ * run beside a GEMM that occupies all of them. Same arguments; no alignment rule. No counterpart in the
+ * reference (single GPU). */
+int mxb_push_block_dma(const void* src, long long src_pitch, void* const* dsts, int copies, long long dst_pitch,
+                       long long rows, long long row_bytes, void* stream);
+
 /* Read (and optionally clear) the device status word of the current device. Synchronises the
  * device. 0 = no kernel reported a problem; otherwise the first recorded code:
  *   0x100 / 0x200 / 0x300 / 0x400  a bounded wait of the TMA producer / of the MMA warp for operands / of the

@@ -44,6 +44,8 @@ EXPORTED_SYMBOLS = (
     "mxb_gemm",
     "mxb_gemm_cfg",
     "mxb_push_block",
+    "mxb_push_block_ex",
+    "mxb_push_block_dma",
     "mxb_gemm_host",
     "mxb_gemm_static_scratch",
     "mxb_block_quant",
@@ -120,6 +122,10 @@ def _load() -> ctypes.CDLL:
     lib.mxb_push_block.restype = ctypes.c_int
     lib.mxb_push_block.argtypes = [vp, ctypes.c_longlong, ctypes.POINTER(vp), ctypes.c_int, ctypes.c_longlong,
                                    ctypes.c_longlong, ctypes.c_longlong, vp]
+    lib.mxb_push_block_ex.restype = ctypes.c_int
+    lib.mxb_push_block_ex.argtypes = lib.mxb_push_block.argtypes[:-1] + [ctypes.c_int, vp]
+    lib.mxb_push_block_dma.restype = ctypes.c_int
+    lib.mxb_push_block_dma.argtypes = lib.mxb_push_block.argtypes
     lib.mxb_gemm_host.restype = ctypes.c_int
     lib.mxb_gemm_host.argtypes = [pp, vp, vp, vp, vp, vp, vp]
     lib.mxb_gemm_static_scratch.restype = ctypes.c_int

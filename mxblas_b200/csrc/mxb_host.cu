@@ -341,7 +341,9 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
   const int tiles = pl.tiles_x * pl.tiles_y;
   int splits = cfg && cfg->splits > 0 ? cfg->splits : skinny_splits;
   // promotion kernels split K only where every slice starts on a scale group (groups of at most one K block)
-  const bool split_ok = !(pl.scale_mode == SCALE_PROMOTE && q.sk > 128) && !(pl.out_mode == OUT_QUANT_X && q.qn > 32);
+  // (K slices start on 128-wide K blocks, so a scale group must divide 128: 32, 64 or 128)
+  const bool split_ok = !(pl.scale_mode == SCALE_PROMOTE && (q.sk > 128 || 128 % q.sk != 0)) &&
+                        !(pl.out_mode == OUT_QUANT_X && q.qn > 32);
   if (splits == 0) {
     splits = 1;
     // Split-K pays only when the tiles alone cannot occupy the GPU (measured on B200: with 224 tiles on
@@ -642,14 +644,24 @@ static int run_gemm(const mxb_problem_t& q, const mxb_config_t* cfg, const void*
   if (pl.probe) {
     // twin launch for scales that turned out not to be powers of two: same problem through the
     // register-promotion kernel, gated on the flag the packing kernels raised
+    // The twin is a one-CTA kernel on 128-row tiles whatever the first launch was: its tile grid, raster and
+    // K slicing are its own (a CTA-pair plan counts 256-row tiles and may slice its last wave).
     LaunchArgs fb = la;
     fb.p.gate_value = 1;
     fb.p.splits = 1;
+    fb.p.tail_splits = 1;
+    fb.p.ws_partial = nullptr;
+    fb.p.ws_count = nullptr;
+    fb.p.tiles_x = (pl.rx + 127) / 128;
     fb.p.tiles_y = (pl.ry + pl.fallback_bn - 1) / pl.fallback_bn;
+    fb.p.tail_first = fb.p.tiles_x * fb.p.tiles_y;
+    fb.p.raster = cfg && cfg->raster > 0 ? cfg->raster : 8;
+    if (fb.p.raster > fb.p.tiles_x) fb.p.raster = fb.p.tiles_x;
     st = operand_map(yp, pl.ry, q.k, ypitch, pl.fallback_bn, &fb.tm_y);
     if (st != MXB_OK) return st;
-    const int fb_units = fb.p.tiles_x * fb.p.tiles_y;
-    fb.grid = fb_units < pl.ctas ? fb_units : pl.ctas;
+    const long long fb_units = static_cast<long long>(fb.p.tiles_x) * fb.p.tiles_y;
+    const long long fb_slots = static_cast<long long>(pl.ctas) * pl.fallback->ctas_per_sm;
+    fb.grid = static_cast<int>(fb_units < fb_slots ? fb_units : fb_slots);
     e = pl.fallback->fn(fb);
     if (e != cudaSuccess) return cuda_fail(e, "mx_gemm_sm100 fallback launch");
     g_launches.fetch_add(1, std::memory_order_relaxed);

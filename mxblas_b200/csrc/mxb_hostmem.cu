@@ -29,17 +29,21 @@ struct DeviceState {
   bool init = false;
 };
 
-std::mutex g_mu;
+// one lock per device: calls for different GPUs of one process run side by side, calls for the same GPU
+// share its staging buffers and take turns
+std::mutex g_mu[64];
 DeviceState g_state[64];
 
-bool ensure(Staging& s, size_t bytes, bool zero = false) {
+// `zero_on` != nullptr: the new buffer is zero-filled on that stream (the GEMMs that read the workspace's
+// counters run on it, so the fill is ordered in front of them)
+bool ensure(Staging& s, size_t bytes, cudaStream_t zero_on = nullptr) {
   if (bytes == 0) bytes = 256;
   if (s.bytes >= bytes) return true;
   if (s.ptr) cudaFree(s.ptr);
   s.ptr = nullptr;
   s.bytes = 0;
   if (cudaMalloc(&s.ptr, bytes) != cudaSuccess) return false;
-  if (zero && cudaMemset(s.ptr, 0, bytes) != cudaSuccess) return false;
+  if (zero_on != nullptr && cudaMemsetAsync(s.ptr, 0, bytes, zero_on) != cudaSuccess) return false;
   s.bytes = bytes;
   return true;
 }
@@ -67,7 +71,7 @@ extern "C" int mxb_gemm_host(const mxb_problem_t* problem, const void* left, con
 
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev >= 64) return MXB_ERR_CUDA;
-  std::lock_guard<std::mutex> lock(g_mu);
+  std::lock_guard<std::mutex> lock(g_mu[dev]);
   DeviceState& d = g_state[dev];
   if (!d.init) {
     if (cudaStreamCreateWithFlags(&d.h2d, cudaStreamNonBlocking) != cudaSuccess) return MXB_ERR_CUDA;
@@ -126,12 +130,19 @@ extern "C" int mxb_gemm_host(const mxb_problem_t* problem, const void* left, con
   if (!ensure(d.left, static_cast<size_t>(q.m) * q.k) || !ensure(d.right, static_cast<size_t>(q.n) * q.k) ||
       !ensure(d.out, static_cast<size_t>(q.m) * q.n * esz_out) || !ensure(d.ls, ls_rows * ls_cols * ssz) ||
       !ensure(d.rs, rs_rows * ls_cols * ssz) ||
-      !ensure(d.os, quant ? static_cast<size_t>(q.m) * groups * ssz : 0) || !ensure(d.ws, ws_bytes, true))
+      !ensure(d.os, quant ? static_cast<size_t>(q.m) * groups * ssz : 0) || !ensure(d.ws, ws_bytes, d.compute))
     return MXB_ERR_CUDA;
 
+  // every enqueue's return code is kept: the first failure ends the call with MXB_ERR_CUDA after the
+  // streams have drained
+  cudaError_t first_err = cudaSuccess;
+  auto ck = [&](cudaError_t e) {
+    if (e != cudaSuccess && first_err == cudaSuccess) first_err = e;
+  };
+
   // scales first (small), then the operand blocks
-  cudaMemcpyAsync(d.rs.ptr, right_scale, rs_rows * ls_cols * ssz, cudaMemcpyHostToDevice, d.h2d);
-  cudaMemcpyAsync(d.ls.ptr, left_scale, ls_rows * ls_cols * ssz, cudaMemcpyHostToDevice, d.h2d);
+  ck(cudaMemcpyAsync(d.rs.ptr, right_scale, rs_rows * ls_cols * ssz, cudaMemcpyHostToDevice, d.h2d));
+  ck(cudaMemcpyAsync(d.ls.ptr, left_scale, ls_rows * ls_cols * ssz, cudaMemcpyHostToDevice, d.h2d));
 
   bool launched[8][8] = {};
   int cols_done[8] = {};
@@ -142,8 +153,8 @@ extern "C" int mxb_gemm_host(const mxb_problem_t* problem, const void* left, con
         if (launched[i][j]) continue;
         launched[i][j] = true;
         const size_t row0 = static_cast<size_t>(i) * mb, col0 = static_cast<size_t>(j) * nb;
-        cudaStreamWaitEvent(d.compute, d.in_ready[i], 0);
-        cudaStreamWaitEvent(d.compute, d.in_ready[8 + j], 0);
+        ck(cudaStreamWaitEvent(d.compute, d.in_ready[i], 0));
+        ck(cudaStreamWaitEvent(d.compute, d.in_ready[8 + j], 0));
         const size_t ls_off = (row0 / q.sm) * static_cast<size_t>(q.as_rs) * ssz;
         const size_t rs_off = (col0 / q.sn) * static_cast<size_t>(q.bs_rs) * ssz;
         char* out_b = static_cast<char*>(d.out.ptr) + (row0 * q.n + col0) * esz_out;
@@ -153,17 +164,17 @@ extern "C" int mxb_gemm_host(const mxb_problem_t* problem, const void* left, con
                       quant ? os_b : nullptr, ws_bytes ? d.ws.ptr : nullptr, ws_bytes, d.compute);
         if (st != MXB_OK) break;
         cudaEvent_t done = d.gemm_done[i * 8 + j];
-        cudaEventRecord(done, d.compute);
-        cudaStreamWaitEvent(d.d2h, done, 0);
-        cudaMemcpy2DAsync(static_cast<char*>(out) + (row0 * q.n + col0) * esz_out, static_cast<size_t>(q.n) * esz_out,
+        ck(cudaEventRecord(done, d.compute));
+        ck(cudaStreamWaitEvent(d.d2h, done, 0));
+        ck(cudaMemcpy2DAsync(static_cast<char*>(out) + (row0 * q.n + col0) * esz_out, static_cast<size_t>(q.n) * esz_out,
                           out_b, static_cast<size_t>(q.n) * esz_out, static_cast<size_t>(nb) * esz_out, mb,
-                          cudaMemcpyDeviceToHost, d.d2h);
+                          cudaMemcpyDeviceToHost, d.d2h));
         // output scales: rows of a block are only (nb / qn) scales long, too short for efficient DMA, so they
         // go back per row block, whole rows at a time, once the row block's last column block is done
         if (quant && ++cols_done[i] == bn)
-          cudaMemcpyAsync(static_cast<char*>(out_scale) + row0 * groups * ssz,
+          ck(cudaMemcpyAsync(static_cast<char*>(out_scale) + row0 * groups * ssz,
                           static_cast<char*>(d.os.ptr) + row0 * groups * ssz, static_cast<size_t>(mb) * groups * ssz,
-                          cudaMemcpyDeviceToHost, d.d2h);
+                          cudaMemcpyDeviceToHost, d.d2h));
       }
   };
   // with out_transpose (or transposed scales) there is one block and the results are copied back whole below
@@ -173,36 +184,36 @@ extern "C" int mxb_gemm_host(const mxb_problem_t* problem, const void* left, con
     const bool send_a = sent_a < bm && (sent_b >= bn || sent_a * bn <= sent_b * bm);
     if (send_a) {
       const size_t row0 = static_cast<size_t>(sent_a) * mb;
-      cudaMemcpyAsync(static_cast<char*>(d.left.ptr) + row0 * q.k, static_cast<const char*>(left) + row0 * q.k,
-                      static_cast<size_t>(mb) * q.k, cudaMemcpyHostToDevice, d.h2d);
-      cudaEventRecord(d.in_ready[sent_a], d.h2d);
+      ck(cudaMemcpyAsync(static_cast<char*>(d.left.ptr) + row0 * q.k, static_cast<const char*>(left) + row0 * q.k,
+                      static_cast<size_t>(mb) * q.k, cudaMemcpyHostToDevice, d.h2d));
+      ck(cudaEventRecord(d.in_ready[sent_a], d.h2d));
       ++sent_a;
     } else {
       const size_t col0 = static_cast<size_t>(sent_b) * nb;
-      cudaMemcpyAsync(static_cast<char*>(d.right.ptr) + col0 * q.k, static_cast<const char*>(right) + col0 * q.k,
-                      static_cast<size_t>(nb) * q.k, cudaMemcpyHostToDevice, d.h2d);
-      cudaEventRecord(d.in_ready[8 + sent_b], d.h2d);
+      ck(cudaMemcpyAsync(static_cast<char*>(d.right.ptr) + col0 * q.k, static_cast<const char*>(right) + col0 * q.k,
+                      static_cast<size_t>(nb) * q.k, cudaMemcpyHostToDevice, d.h2d));
+      ck(cudaEventRecord(d.in_ready[8 + sent_b], d.h2d));
       ++sent_b;
     }
     if (!whole) launch_ready();
   }
   if (whole && st == MXB_OK) {
-    cudaStreamWaitEvent(d.compute, d.in_ready[0], 0);
-    cudaStreamWaitEvent(d.compute, d.in_ready[8], 0);
+    ck(cudaStreamWaitEvent(d.compute, d.in_ready[0], 0));
+    ck(cudaStreamWaitEvent(d.compute, d.in_ready[8], 0));
     st = mxb_gemm(&sub, d.left.ptr, d.right.ptr, d.out.ptr, d.ls.ptr, d.rs.ptr, quant ? d.os.ptr : nullptr,
                   ws_bytes ? d.ws.ptr : nullptr, ws_bytes, d.compute);
     if (st == MXB_OK) {
-      cudaEventRecord(d.gemm_done[0], d.compute);
-      cudaStreamWaitEvent(d.d2h, d.gemm_done[0], 0);
-      cudaMemcpyAsync(out, d.out.ptr, static_cast<size_t>(q.m) * q.n * esz_out, cudaMemcpyDeviceToHost, d.d2h);
+      ck(cudaEventRecord(d.gemm_done[0], d.compute));
+      ck(cudaStreamWaitEvent(d.d2h, d.gemm_done[0], 0));
+      ck(cudaMemcpyAsync(out, d.out.ptr, static_cast<size_t>(q.m) * q.n * esz_out, cudaMemcpyDeviceToHost, d.d2h));
       if (quant)
-        cudaMemcpyAsync(out_scale, d.os.ptr, static_cast<size_t>(q.m) * groups * ssz, cudaMemcpyDeviceToHost, d.d2h);
+        ck(cudaMemcpyAsync(out_scale, d.os.ptr, static_cast<size_t>(q.m) * groups * ssz, cudaMemcpyDeviceToHost, d.d2h));
     }
   }
   cudaError_t e1 = cudaStreamSynchronize(d.h2d);
   cudaError_t e2 = cudaStreamSynchronize(d.compute);
   cudaError_t e3 = cudaStreamSynchronize(d.d2h);
   if (st != MXB_OK) return st;
-  if (e1 != cudaSuccess || e2 != cudaSuccess || e3 != cudaSuccess) return MXB_ERR_CUDA;
+  if (first_err != cudaSuccess || e1 != cudaSuccess || e2 != cudaSuccess || e3 != cudaSuccess) return MXB_ERR_CUDA;
   return MXB_OK;
 }

@@ -113,6 +113,10 @@ mx_gemm_sm100_pair(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   constexpr int STAGES = Cfg::STAGES;
   constexpr int NUM_ACC = Cfg::NUM_ACC;
 
+  // device-side dispatch of a probed call: both CTAs of every pair read the same word, so a pair leaves
+  // together, before anything is signalled across it
+  if (p.gate != nullptr && *p.gate != p.gate_value) return;
+
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;

@@ -39,8 +39,9 @@ __global__ void __launch_bounds__(256) push_block_kernel(const uint8_t* __restri
 
 }  // namespace
 
-extern "C" int mxb_push_block(const void* src, long long src_pitch, void* const* dsts, int copies,
-                              long long dst_pitch, long long rows, long long row_bytes, void* stream) {
+extern "C" int mxb_push_block_ex(const void* src, long long src_pitch, void* const* dsts, int copies,
+                                 long long dst_pitch, long long rows, long long row_bytes, int max_blocks,
+                                 void* stream) {
   if (src == nullptr || dsts == nullptr || copies < 0 || copies > 7 || rows < 0 || row_bytes < 0) return MXB_ERR_INVALID;
   if (copies == 0 || rows == 0 || row_bytes == 0) return MXB_OK;
   if (row_bytes % 16 || src_pitch % 16 || dst_pitch % 16 || (reinterpret_cast<uintptr_t>(src) & 15))
@@ -58,8 +59,31 @@ extern "C" int mxb_push_block(const void* src, long long src_pitch, void* const*
   if (vec_per_row > 0x7fffffffll) return MXB_ERR_UNSUPPORTED;
   const long long total = rows * vec_per_row;
   long long blocks = (total + 255) / 256;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (max_blocks <= 0) max_blocks = 148 * 8;
+  if (blocks > max_blocks) blocks = max_blocks;
   push_block_kernel<<<static_cast<unsigned int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint8_t*>(src), src_pitch, d, dst_pitch, rows, static_cast<int>(vec_per_row));
   return cudaGetLastError() == cudaSuccess ? MXB_OK : MXB_ERR_CUDA;
+}
+
+extern "C" int mxb_push_block(const void* src, long long src_pitch, void* const* dsts, int copies,
+                              long long dst_pitch, long long rows, long long row_bytes, void* stream) {
+  return mxb_push_block_ex(src, src_pitch, dsts, copies, dst_pitch, rows, row_bytes, 0, stream);
+}
+
+// The same transfer on the copy engines: one 2-D copy per destination. Needs no SM, so it runs beside a
+// persistent GEMM that occupies all of them.
+extern "C" int mxb_push_block_dma(const void* src, long long src_pitch, void* const* dsts, int copies,
+                                  long long dst_pitch, long long rows, long long row_bytes, void* stream) {
+  if (src == nullptr || dsts == nullptr || copies < 0 || copies > 7 || rows < 0 || row_bytes < 0) return MXB_ERR_INVALID;
+  if (copies == 0 || rows == 0 || row_bytes == 0) return MXB_OK;
+  if (src_pitch < row_bytes || dst_pitch < row_bytes) return MXB_ERR_INVALID;
+  for (int i = 0; i < copies; ++i) {
+    if (dsts[i] == nullptr) return MXB_ERR_INVALID;
+    cudaError_t e = cudaMemcpy2DAsync(dsts[i], static_cast<size_t>(dst_pitch), src, static_cast<size_t>(src_pitch),
+                                      static_cast<size_t>(row_bytes), static_cast<size_t>(rows),
+                                      cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return MXB_ERR_CUDA;
+  }
+  return MXB_OK;
 }

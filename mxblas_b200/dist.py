@@ -110,10 +110,12 @@ def sharded_mx_gemm(
     ``right_is_local`` says they already are this rank's shard. Returns this rank's column block of
     the result, or, with ``gather=True``, the full result on every rank (one NCCL all-gather per
     output tensor). ``gather="peer"`` produces the same full result without a collective: the result lives in
-    symmetric memory, each rank's GEMM writes its column block of its own copy and a copy kernel then pushes
-    the block into every other rank's copy (plain stores over NVLink, at the block's place in the final layout),
-    followed by one cross-rank barrier on the stream. The tensors
-    returned are views of buffers that the next ``gather="peer"`` call of the same shape reuses.
+    symmetric memory, each rank's GEMM writes its column block of its own copy and the block is then pushed
+    into every other rank's copy (plain stores over NVLink from a copy kernel, or the copy engines with
+    ``peer_transport="dma"``), at its place in the final layout, followed by one cross-rank barrier on the
+    stream. Large row-major results are produced in row chunks (``peer_chunks``), the push of one chunk running
+    under the GEMM of the next. Column blocks that are not 16-byte aligned take the all-gather instead. The
+    tensors returned are views of buffers that the next ``gather="peer"`` call of the same shape reuses.
     ``compute`` replaces the local GEMM (tests run the host logic on CPU ranks).
     """
     if compute is None:
@@ -157,8 +159,11 @@ def _symmetric(shape, dtype, group, tag):
     return hit
 
 
-def _push(block: torch.Tensor, full: torch.Tensor, hdl, world: int, rank: int) -> None:
-    """This rank's block (a view of its symmetric tensor ``full``) into the same place of every peer's copy."""
+def _push(block: torch.Tensor, full: torch.Tensor, hdl, world: int, rank: int, dma: bool = False,
+          max_blocks: int = 0) -> None:
+    """This rank's block (a view of its symmetric tensor ``full``) into the same place of every peer's copy, on
+    the current stream: by a copy kernel (stores over NVLink; ``max_blocks`` bounds its grid) or, with ``dma``,
+    by the copy engines."""
     import ctypes
 
     from . import _ext
@@ -168,10 +173,45 @@ def _push(block: torch.Tensor, full: torch.Tensor, hdl, world: int, rank: int) -
     esz = block.element_size()
     ptrs = (ctypes.c_void_p * len(peers))(*peers)
     stream = torch._C._cuda_getCurrentRawStream(block.device.index)
-    st = _ext.lib.mxb_push_block(block.data_ptr(), block.stride(0) * esz, ptrs, len(peers), block.stride(0) * esz,
-                                 block.shape[0], block.shape[1] * esz, stream)
+    geom = (block.data_ptr(), block.stride(0) * esz, ptrs, len(peers), block.stride(0) * esz, block.shape[0],
+            block.shape[1] * esz)
+    if dma:
+        st = _ext.lib.mxb_push_block_dma(*geom, stream)
+    else:
+        st = _ext.lib.mxb_push_block_ex(*geom, max_blocks, stream)
     if st != _ext.MXB_OK:
         raise RuntimeError("mxb_push_block: " + _ext.status_text(st))
+
+
+def _pushable(block: torch.Tensor) -> bool:
+    esz = block.element_size()
+    return (block.shape[1] * esz) % 16 == 0 and (block.stride(0) * esz) % 16 == 0 and block.data_ptr() % 16 == 0
+
+
+_side_streams: dict = {}
+
+
+def _side_stream(device: torch.device) -> torch.cuda.Stream:
+    s = _side_streams.get(device.index)
+    if s is None:
+        s = _side_streams[device.index] = torch.cuda.Stream(device=device)
+    return s
+
+
+def peer_row_chunks(m: int, sm: int, out_transpose: bool, transposed_scales: bool, want: Optional[int] = None) -> int:
+    """Into how many row chunks of ``left`` a gather="peer" call is cut so that the push of one chunk's result
+    runs under the GEMM of the next: chunks of whole 256-row tiles and whole scale blocks of at least 2048 rows,
+    at most 8; one chunk for transposed results (a row chunk of left is a column strip of C^T, too narrow to
+    store or push efficiently)."""
+    if out_transpose or transposed_scales or m < 4096:
+        return 1
+    chunks = want or min(8, m // 2048)
+    while chunks > 1:
+        mc = m // chunks
+        if m % chunks == 0 and mc % 256 == 0 and (sm == m or mc % sm == 0):
+            break
+        chunks -= 1
+    return max(chunks, 1)
 
 
 def _peer_gathered(left, right, left_scale, right_scale, output_quant, quant_size, out_dtype, out_transpose,
@@ -190,80 +230,62 @@ def _peer_gathered(left, right, left_scale, right_scale, output_quant, quant_siz
         sc_mine = sc_full[g0 : g0 + gl] if out_scale_transpose else sc_full[:, g0 : g0 + gl]
     else:
         sc_mine = torch.empty([], dtype=left_scale.dtype, device=left.device)
+    # the alignment rule of the push is a property of the shapes: decided before anything is enqueued, the
+    # same on every rank, so an unaligned problem takes the all-gather everywhere
+    if not (_pushable(mine) and (not output_quant or _pushable(sc_mine))):
+        out, out_scale = compute(left, right, left_scale, right_scale, output_quant, quant_size, out_dtype,
+                                 out_transpose, out_scale_transpose, **kwargs)
+        out = gather_columns(out, out_transpose, group)
+        if output_quant:
+            out_scale = gather_columns(out_scale, out_scale_transpose, group)
+        return out, out_scale
+    kwargs = dict(kwargs)
+    dma = kwargs.pop("peer_transport", "sm") == "dma"
+    sm_rows = m // left_scale.shape[0]
+    chunks = peer_row_chunks(m, sm_rows, out_transpose, output_quant and out_scale_transpose,
+                             kwargs.pop("peer_chunks", None))
     hdl.barrier(channel=0)  # every rank is done with the previous contents of the buffers
-    compute(left, right, left_scale, right_scale, output_quant, quant_size, out_dtype, out_transpose,
-            out_scale_transpose, _into=(mine, sc_mine), **kwargs)
-    ok = (mine.shape[1] * mine.element_size()) % 16 == 0 and (mine.stride(0) * mine.element_size()) % 16 == 0
-    if output_quant:
-        ok = ok and (sc_mine.shape[1] * sc_mine.element_size()) % 16 == 0 and \
-            (sc_mine.stride(0) * sc_mine.element_size()) % 16 == 0 and sc_mine.data_ptr() % 16 == 0
-    if not ok or mine.data_ptr() % 16:
-        raise ValueError("gather='peer' needs 16-byte aligned column blocks")
-    _push(mine, full, hdl, world, rank)
-    if output_quant:
-        _push(sc_mine, sc_full, sc_hdl, world, rank)
+    if chunks == 1:
+        compute(left, right, left_scale, right_scale, output_quant, quant_size, out_dtype, out_transpose,
+                out_scale_transpose, _into=(mine, sc_mine), **kwargs)
+        _push(mine, full, hdl, world, rank, dma)
+        if output_quant:
+            _push(sc_mine, sc_full, sc_hdl, world, rank, dma)
+    else:
+        # Row chunks: the GEMM of chunk i+1 runs on the caller's stream while chunk i's block crosses NVLink on a
+        # side stream. The copy kernel needs SMs of its own (a persistent GEMM CTA fills an SM's registers and
+        # shared memory), so the GEMMs run on all SMs but `reserve`; the copy engines need none.
+        main = torch.cuda.current_stream()
+        side = _side_stream(left.device)
+        if not dma and "config" not in kwargs:
+            from ._ext import MxbConfig
+
+            sms = torch.cuda.get_device_properties(left.device).multi_processor_count
+            kwargs["config"] = MxbConfig(0, -1, 0, 0, 0, (sms - PEER_PUSH_SMS) & ~1, 0)
+        mc = m // chunks
+        for i in range(chunks):
+            r0, r1 = i * mc, (i + 1) * mc
+            ls_i = left_scale if sm_rows == m else left_scale[r0 // sm_rows : r1 // sm_rows]
+            blk = mine[r0:r1]
+            sc_blk = sc_mine[r0:r1] if output_quant else sc_mine
+            compute(left[r0:r1], right, ls_i, right_scale, output_quant, quant_size, out_dtype, False,
+                    False, _into=(blk, sc_blk), **kwargs)
+            done = torch.cuda.Event()
+            done.record(main)
+            side.wait_event(done)
+            with torch.cuda.stream(side):
+                _push(blk, full, hdl, world, rank, dma, 8 * PEER_PUSH_SMS)
+                if output_quant:
+                    _push(sc_blk, sc_full, sc_hdl, world, rank, dma, 8 * PEER_PUSH_SMS)
+        main.wait_stream(side)
     hdl.barrier(channel=1)  # every rank's block has landed everywhere
     return full, (sc_full if output_quant else sc_mine)
 
 
-# -------------------------------------------------------------------------------------------------
-# Strong-scaling measurement of a BASELINE configuration (total N fixed, N/g columns per rank):
-#   python -m torch.distributed.run --nnodes=1 --nproc-per-node G --master-addr 127.0.0.1 \
-#       -m mxblas_b200.dist --config c5 --rows 16
-# Rank 0 prints one JSON line: GEMM time (max over ranks, CUDA events) and GEMM + all-gather time.
-# -------------------------------------------------------------------------------------------------
-def _bench_cli() -> None:
-    import argparse
-    import json
-    import os
-
-    from .tune import baseline_problem
-
-    ap = argparse.ArgumentParser(description="N-sharded timing of one BASELINE configuration")
-    ap.add_argument("--config", choices=["c2", "c3", "c4", "c5"], required=True)
-    ap.add_argument("--rows", type=int, default=None, help="M of config c5 (torchrun claims every --m… prefix)")
-    ap.add_argument("--iters", type=int, default=20)
-    a = ap.parse_args()
-    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
-    local = int(os.environ.get("LOCAL_RANK", rank))
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    args, kw, flops, nbytes, shape = baseline_problem(a.config, a.rows, device=f"cuda:{local}", shard=world)
-    flush = torch.zeros(256 << 20, dtype=torch.uint8, device=f"cuda:{local}")
-
-    def timed(gather: bool) -> float:
-        times = []
-        if world > 1:
-            dist.barrier()
-        for it in range(a.iters + 3):
-            # evict the operands from L2; the read also keeps the GPU busy while the host enqueues the call,
-            # so that no launch latency lands between the events
-            flush.sum()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            sharded_mx_gemm(*args, gather=gather, right_is_local=True, **kw)
-            e1.record()
-            torch.cuda.synchronize()
-            if it >= 3:
-                times.append(e0.elapsed_time(e1) * 1e-3)
-        times.sort()
-        t = torch.tensor([times[len(times) // 2]], device=f"cuda:{local}")
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    t_gemm = timed(False)
-    t_all = timed(True)
-    t_peer = timed("peer") if world > 1 else t_gemm
-    if rank == 0:
-        print(json.dumps({"config": a.config, "per_rank_shape": list(shape), "n_gpus": world,
-                          "gemm_us": t_gemm * 1e6, "gemm_plus_gather_us": t_all * 1e6,
-                          "gemm_plus_peer_push_us": t_peer * 1e6,
-                          "whole_job_tflops": flops * world / t_gemm / 1e12}), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+PEER_PUSH_SMS = 20  # SMs left to the copy kernel while a chunked gather="peer" call's GEMMs run
 
 
 if __name__ == "__main__":
-    _bench_cli()
+    from .bench_configs import dist_main
+
+    dist_main()

@@ -301,13 +301,17 @@ def mx_gemm_kernel(
             ldcs = 0
     problem = make_problem(meta, out.stride(0), ldcs, out_scale_pow2, pow2_scales)
     if config is None:
-        tune = _tune_module()  # the persisted autotune table (mxblas/gemm/kernel_pool.py:85-89 is in-memory only)
-        if tune.ENABLED:
-            config = tune.lookup(meta, out_scale_pow2, pow2_scales)
-            if config is None and not torch.cuda.is_current_stream_capturing():
-                config, _ = tune.autotune(
-                    left, right, left_scale, right_scale, output_quant, quant_size, out_dtype, out_transpose,
-                    out_scale_transpose, out_scale_pow2=out_scale_pow2, pow2_scales=pow2_scales)
+        # tuned plans (mxblas/gemm/kernel_pool.py:85-89 keeps its winners in memory only; here they persist)
+        tune = _tune_module()
+        if tune.USE_TABLES:
+            config = tune.plan_for(meta, out_scale_pow2, pow2_scales)
+            if config is None and tune.ENABLED and not torch.cuda.is_current_stream_capturing():
+                key = tune.table_key(meta, out_scale_pow2, pow2_scales)
+                if key not in tune._load_table():
+                    tune.autotune(
+                        left, right, left_scale, right_scale, output_quant, quant_size, out_dtype, out_transpose,
+                        out_scale_transpose, out_scale_pow2=out_scale_pow2, pow2_scales=pow2_scales)
+                    config = tune.plan_for(meta, out_scale_pow2, pow2_scales)
     cfg_ptr = ctypes.byref(config) if config is not None else None
     # Host time per call matters for the small problems (a decode step's kernel takes 20-40 us): the raw
     # stream handle instead of a Stream object, no device guard when the device is already current, and the

@@ -1,30 +1,33 @@
-"""Tile / CTA-pair / split-K autotuner and shape benchmark.
+"""Tile / CTA-pair / split-K autotuner.
 
 Stands where the reference has ``JITTuner.compile_and_tune`` (mxblas/jit/tuner.py:59-182), which
-compiles every candidate of a 57 344-point space with nvcc and times it with kineto, and
-``build_tunning_space`` (mxblas/jit_kernels/mx_gemm.py:197-291). Here every kernel variant is already
-in the library, a candidate is just an ``MxbConfig``, a few dozen of them are timed with CUDA events,
-and the winner is persisted (the reference re-tunes in every process):
+compiles every candidate of a 57 344-point space with nvcc and times it with kineto,
+``build_tunning_space`` (mxblas/jit_kernels/mx_gemm.py:197-291) and the in-memory kernel pool
+(mxblas/gemm/kernel_pool.py:79-186). Here every kernel variant is already in the library, a candidate
+is just an ``MxbConfig``, a few dozen of them are timed with CUDA events, and the winner is persisted
+(the reference re-tunes in every process).
 
-    MXBLAS_CACHE_DIR/autotune_<gpu>.json     key = dtypes, (M bucket, N, K), scale granularity, quant, flags
+Which plan a call without an explicit ``config`` gets:
+  1. the entry of the user's table  MXBLAS_CACHE_DIR/autotune_<gpu>.json  for the problem's key
+     (dtypes, M bucket, N, K, scale granularity, quantisation, flags), if there is one;
+  2. else the entry of the table shipped with the package (mxblas_b200/tuned/<gpu>.json: the BASELINE
+     shapes, tuned on a B200);
+  3. else, with ``MXBLAS_B200_AUTOTUNE=1`` and outside a stream capture, the problem is tuned on the spot
+     and the winner stored in the user's table;
+  4. else the library's heuristic plan (choose_plan in csrc/mxb_host.cu).
+``MXBLAS_B200_TABLES=0`` skips 1-3. The table is shared by all threads of the process behind one lock;
+the file is replaced atomically, so concurrent processes never read a torn table.
 
-``MXBLAS_B200_AUTOTUNE=1`` makes ``mx_gemm_kernel`` consult and fill this table for calls without an
-explicit ``config``; ``MXBLAS_PRINT_AUTO_TUNE=1`` prints every timed candidate and
-``MXBLAS_PROFILING_TIME_PATH`` appends them to a file, as in the reference.
-
-Command line (also the committed driver of the numbers in profiles/):
-
-    python -m mxblas_b200.tune --config c2            # time the default plan of a BASELINE config
-    python -m mxblas_b200.tune --config c5 --m 16 --sweep   # time every candidate
-    python -m mxblas_b200.tune --all                  # one line per BASELINE config (JSON)
+``MXBLAS_PRINT_AUTO_TUNE=1`` prints every timed candidate and ``MXBLAS_PROFILING_TIME_PATH`` appends
+them to a file, as in the reference. Command lines that time the BASELINE configurations live in
+mxblas_b200/bench_configs.py (``python -m mxblas_b200.tune ...`` forwards there).
 """
 
 from __future__ import annotations
 
-import argparse
-import ctypes
 import json
 import os
+import threading
 from pathlib import Path
 from typing import Callable, Iterable, List, Optional, Tuple
 
@@ -34,8 +37,13 @@ from . import _ext
 from ._ext import MxbConfig
 from .const import CACHE_DIR_FLAG, PRINT_AUTOTUNE_FLAG, PROFILING_TIME_PATH
 
-ENABLED = os.environ.get("MXBLAS_B200_AUTOTUNE", "0") not in ("", "0")
-_table: Optional[dict] = None
+ENABLED = os.environ.get("MXBLAS_B200_AUTOTUNE", "0") not in ("", "0")  # tune unknown problems on first use
+USE_TABLES = os.environ.get("MXBLAS_B200_TABLES", "1") not in ("", "0")  # consult the persisted tables
+AUTO = (0, -1, 0, 0, 0, 0, 0)  # MxbConfig fields that leave every choice to the library's heuristic
+_table: Optional[dict] = None      # user's table (read-write)
+_shipped: Optional[dict] = None    # table shipped with the package (read-only)
+_lock = threading.RLock()          # guards both tables, the plan cache and the file
+_plan_cache: dict = {}             # (meta, flags) -> MxbConfig or None, so a warm call costs one dict lookup
 _flush_buf: Optional[torch.Tensor] = None
 
 
@@ -70,11 +78,15 @@ def time_call(fn: Callable[[], object], iters: int = 10, warmup: int = 3, flush_
 # candidates
 # -------------------------------------------------------------------------------------------------
 def candidates(m: int, n: int, k: int, sk: int, quant: bool, out_transpose: bool, mx: bool) -> List[MxbConfig]:
-    """Configurations worth timing for a problem; invalid ones are filtered by the library."""
-    out: List[MxbConfig] = []
+    """Configurations worth timing for a problem; the library filters out the ones it has no kernel for.
+    The first candidate is always the heuristic plan itself, so the winner is never slower than it.
+    Fields: (bn, swap, epi_warps, raster, splits, ctas, cta_pair); splits 0 lets CTA-pair plans cut the
+    tiles of an incomplete last wave along K, splits 1 forbids it."""
+    out: List[MxbConfig] = [MxbConfig(*AUTO)]
     swap_opts = (1,) if out_transpose else ((1,) if m <= 128 else (0,))
+    big = m > 256
     if sk == k:  # scales constant along K
-        if m <= 256:
+        if not big:
             for swap in ((1,) if m <= 32 else (0, 1)):
                 for bn in (32, 64, 128, 256):
                     ry = m if swap else n
@@ -84,17 +96,27 @@ def candidates(m: int, n: int, k: int, sk: int, quant: bool, out_transpose: bool
                         out.append(MxbConfig(bn, swap, 4, 8, splits, 0, 1))
         else:
             for swap in swap_opts:
-                for raster in (4, 8, 16):
-                    out.append(MxbConfig(256, swap, 8 if quant else 4, raster, 1, 0, 2))
-                    out.append(MxbConfig(256, swap, 8 if quant else 4, raster, 1, 0, 1))
+                for ew in ((4, 8) if quant else (4,)):
+                    for raster in (4, 8, 16, 32):
+                        for tail in (0, 1):
+                            out.append(MxbConfig(256, swap, ew, raster, tail, 0, 2))
+                    out.append(MxbConfig(256, swap, ew, 8, 1, 0, 1))
+                out.append(MxbConfig(224, swap, 4, 16, 1, 0, 2))
                 out.append(MxbConfig(128, swap, 4, 8, 1, 0, 1))
-    elif mx:
+    elif mx:  # 1x32 power-of-two scales on the block-scaled MMA
         for swap in swap_opts:
+            if big:
+                for raster in (4, 8, 16, 32):
+                    out.append(MxbConfig(224, swap, 4, raster, 1, 0, 2))
             for bn in (128, 224):
                 for raster in (4, 8, 16):
                     out.append(MxbConfig(bn, swap, 4, raster, 1, 0, 1))
-    else:  # promotion
+    else:  # scales that change along K: promotion in registers
         for swap in swap_opts:
+            if big and sk == 128:
+                for raster in (4, 8, 16, 32):
+                    for tail in (0, 1):
+                        out.append(MxbConfig(256, swap, 8, raster, tail, 0, 2))
             for bn, ew in ((128, 4), (128, 8), (256, 8), (64, 4)):
                 for raster in (4, 8, 16):
                     out.append(MxbConfig(bn, swap, ew, raster, 1, 0, 1))
@@ -104,28 +126,62 @@ def candidates(m: int, n: int, k: int, sk: int, quant: bool, out_transpose: bool
 # -------------------------------------------------------------------------------------------------
 # persisted table
 # -------------------------------------------------------------------------------------------------
+def _gpu_name() -> str:
+    return torch.cuda.get_device_name().replace(" ", "_") if torch.cuda.is_available() else "cpu"
+
+
 def _table_path() -> Path:
     root = Path(os.environ.get(CACHE_DIR_FLAG, str(Path.home() / ".mxblas_b200")))
-    name = torch.cuda.get_device_name().replace(" ", "_") if torch.cuda.is_available() else "cpu"
-    return root / f"autotune_{name}.json"
+    return root / f"autotune_{_gpu_name()}.json"
+
+
+def _shipped_path() -> Path:
+    return Path(__file__).resolve().parent / "tuned" / f"{_gpu_name()}.json"
+
+
+def _read(path: Path) -> dict:
+    try:
+        return json.loads(path.read_text())
+    except (OSError, ValueError):
+        return {}
 
 
 def _load_table() -> dict:
     global _table
-    if _table is None:
-        try:
-            _table = json.loads(_table_path().read_text())
-        except (OSError, ValueError):
-            _table = {}
-    return _table
+    with _lock:
+        if _table is None:
+            _table = _read(_table_path())
+        return _table
+
+
+def _load_shipped() -> dict:
+    global _shipped
+    with _lock:
+        if _shipped is None:
+            _shipped = _read(_shipped_path())
+        return _shipped
+
+
+def reload_tables() -> None:
+    """Forget what was read from disk (a new process-style start; tests, or after another process tuned)."""
+    global _table, _shipped
+    with _lock:
+        _table = _shipped = None
+        _plan_cache.clear()
 
 
 def _save_table() -> None:
-    path = _table_path()
-    path.parent.mkdir(parents=True, exist_ok=True)
-    tmp = path.with_suffix(f".tmp{os.getpid()}")
-    tmp.write_text(json.dumps(_table, indent=0, sort_keys=True))
-    os.replace(tmp, path)  # atomic, as the reference's cache writes (mxblas/jit/compiler.py:113-118)
+    with _lock:
+        path = _table_path()
+        path.parent.mkdir(parents=True, exist_ok=True)
+        # merge what another process stored meanwhile, then replace the file atomically, as the reference's
+        # cache writes do (mxblas/jit/compiler.py:113-118)
+        merged = _read(path)
+        merged.update(_table or {})
+        _table.update(merged)
+        tmp = path.with_suffix(f".tmp{os.getpid()}.{threading.get_ident()}")
+        tmp.write_text(json.dumps(merged, indent=0, sort_keys=True))
+        os.replace(tmp, path)
 
 
 def m_bucket(m: int) -> int:
@@ -139,13 +195,32 @@ def m_bucket(m: int) -> int:
 def table_key(meta, out_scale_pow2: bool, pow2_scales) -> str:
     return "|".join(str(x) for x in (
         meta.in_dtype, meta.out_dtype, meta.scale_dtype, m_bucket(meta.m), meta.n, meta.k, meta.sm if meta.sm == 1 else
-        "M" if meta.sm == meta.m else meta.sm, meta.sn, meta.sk, meta.qn, int(meta.out_transpose),
+        "M" if meta.sm == meta.m else meta.sm, meta.sn, meta.sk, meta.qm, meta.qn, int(meta.out_transpose),
         int(meta.out_scale_transpose), int(bool(out_scale_pow2)), pow2_scales))
 
 
 def lookup(meta, out_scale_pow2: bool, pow2_scales) -> Optional[MxbConfig]:
-    rec = _load_table().get(table_key(meta, out_scale_pow2, pow2_scales))
-    return MxbConfig(*rec["config"]) if rec else None
+    """The tuned configuration of a problem: user's table first, then the shipped one; None if neither has it
+    (or the entry is the heuristic plan itself)."""
+    key = table_key(meta, out_scale_pow2, pow2_scales)
+    with _lock:
+        rec = _load_table().get(key) or _load_shipped().get(key)
+    if not rec or tuple(rec["config"]) == AUTO:
+        return None
+    return MxbConfig(*rec["config"])
+
+
+def plan_for(meta, out_scale_pow2: bool, pow2_scales) -> Optional[MxbConfig]:
+    """``lookup`` behind a per-process cache keyed by the call signature itself (no string formatting on the
+    warm path)."""
+    ck = (meta, bool(out_scale_pow2), pow2_scales)
+    try:
+        return _plan_cache[ck]
+    except KeyError:
+        cfg = lookup(meta, out_scale_pow2, pow2_scales)
+        with _lock:
+            _plan_cache[ck] = cfg
+        return cfg
 
 
 def autotune(left, right, left_scale, right_scale, output_quant=False, quant_size=None, out_dtype=None,
@@ -184,89 +259,14 @@ def autotune(left, right, left_scale, right_scale, output_quant=False, quant_siz
         raise ValueError("autotune: no candidate configuration ran")
     best_key, best_t = min(results, key=lambda r: r[1])
     if persist:
-        _load_table()[table_key(meta, out_scale_pow2, pow2_scales)] = {"config": list(best_key), "us": best_t * 1e6}
-        _save_table()
+        with _lock:
+            _load_table()[table_key(meta, out_scale_pow2, pow2_scales)] = {"config": list(best_key), "us": best_t * 1e6}
+            _save_table()
+            _plan_cache.clear()
     return MxbConfig(*best_key), results
 
 
-# -------------------------------------------------------------------------------------------------
-# BASELINE configurations (synthetic seeded data of their shapes and value distributions)
-# -------------------------------------------------------------------------------------------------
-def baseline_problem(name: str, m: Optional[int] = None, device="cuda", shard: int = 1):
-    """Operands and call arguments of BASELINE config c1..c5; c4 with shard=8 is one GPU's N slice."""
-    g = torch.Generator(device="cpu").manual_seed(0)
-
-    def fp8(rows, cols, scale=1.0):
-        return (torch.randn(rows, cols, generator=g) * scale).clamp(-448, 448).to(torch.float8_e4m3fn).to(device)
-
-    def uni(rows, cols, lo, hi, dtype=torch.float32):
-        return (lo + (hi - lo) * torch.rand(rows, cols, generator=g)).to(dtype).to(device)
-
-    kw = {}
-    if name in ("c1", "c2"):
-        M = N = K = 256 if name == "c1" else 8192
-        N //= shard
-        sdt = torch.float32 if name == "c1" else torch.bfloat16
-        a, b, sa, sb = fp8(M, K), fp8(N, K), uni(1, 1, 0.5, 2, sdt), uni(1, 1, 0.5, 2, sdt)
-        args = (True, torch.Size((1, 16))) if name == "c2" else ()
-    elif name == "c3":
-        M, N, K = 4096, 7168 // shard, 7168
-        a, b = fp8(M, K, 2.0), fp8(N, K, 2.0)
-        sa, sb = uni(M, K // 128, 1e-3, 1e-1), uni(N // 128, K // 128, 1e-3, 1e-1)
-        args, kw = (), {"pow2_scales": False}
-    elif name == "c4":
-        M, N, K = 16384, 8192 // shard, 8192
-        a, b = fp8(M, K), fp8(N, K)
-        sa = torch.pow(2.0, torch.randint(-8, 5, (M, K // 32), generator=g).float()).to(device)
-        sb = torch.pow(2.0, torch.randint(-8, 5, (N, K // 32), generator=g).float()).to(device)
-        args, kw = (True, torch.Size((1, 32)), None, True), {"out_scale_pow2": True, "pow2_scales": True}
-    elif name == "c5":
-        M, N, K = m or 16, 28672 // shard, 8192
-        a, b, sa, sb = fp8(M, K), fp8(N, K), uni(M, 1, 0.5, 2), uni(N, 1, 0.5, 2)
-        args = ()
-    else:
-        raise ValueError(name)
-    quant = bool(args) and args[0] is True
-    qn = int(args[1][1]) if quant else 0
-    sbytes = sa.element_size()
-    nbytes = (M * K + N * K + M * N * (1 if quant else 2) + (M * (N // qn) * sbytes if quant else 0) +
-              sa.numel() * sbytes + sb.numel() * sbytes)
-    return (a, b.t(), sa, sb.t()) + args, kw, 2.0 * M * N * K, nbytes, (M, N, K)
-
-
-def bench_config(name: str, m: Optional[int] = None, sweep: bool = False, shard: int = 1, iters: int = 10) -> dict:
-    from .mx_gemm import mx_gemm_kernel
-
-    args, kw, flops, nbytes, shape = baseline_problem(name, m, shard=shard)
-    rows = []
-    if sweep:
-        _, results = autotune(*args, **kw, persist=False, iters=iters)
-        rows = [{"config": list(key), "us": t * 1e6} for key, t in sorted(results, key=lambda r: r[1])]
-        med = rows[0]["us"] * 1e-6
-    else:
-        med, _ = time_call(lambda: mx_gemm_kernel(*args, **kw), iters=iters)
-    status = _ext.device_status()
-    return {"config": name, "shape": list(shape), "us": med * 1e6, "tflops": flops / med / 1e12,
-            "pct_of_4500": 100 * flops / med / 4.5e15, "gbs": nbytes / med / 1e9, "algorithmic_bytes": nbytes,
-            "device_status": status, "candidates": rows}
-
-
-def main() -> None:
-    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("--config", choices=["c1", "c2", "c3", "c4", "c5"])
-    ap.add_argument("--m", type=int, default=None, help="M of config c5")
-    ap.add_argument("--shard", type=int, default=1, help="time one GPU's N slice of an N-sharded run")
-    ap.add_argument("--sweep", action="store_true", help="time every candidate configuration")
-    ap.add_argument("--all", action="store_true", help="all BASELINE configs with the default plans")
-    ap.add_argument("--iters", type=int, default=10)
-    a = ap.parse_args()
-    if a.all:
-        for name, m, shard in [("c1", None, 1), ("c2", None, 1), ("c3", None, 1), ("c4", None, 1), ("c4", None, 8)] + \
-                [("c5", mm, 1) for mm in (16, 64, 256, 1024, 4096, 16384)]:
-            print(json.dumps(bench_config(name, m, False, shard, a.iters)), flush=True)
-    else:
-        print(json.dumps(bench_config(a.config or "c2", a.m, a.sweep, a.shard, a.iters)))
-
-
 if __name__ == "__main__":
+    from .bench_configs import main
+
     main()
