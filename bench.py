@@ -2,7 +2,7 @@
 
 Workload: BASELINE configuration 2 -- M=N=K=8192, per-tensor scales (bf16 [1,1]), fused output
 quantisation to e4m3 in [1,16] groups with bf16 scales. One step = one call of the operator on one
-batch of synthetic operands resident in HBM. With N>1 the SAME problem is sharded along N (strong
+batch of synthetic operands resident in HBM; L2 is flushed between the timed steps. With N>1 the SAME problem is sharded along N (strong
 scaling): every rank holds `left` and the rows [r*8192/N, (r+1)*8192/N) of the physical [N, K]
 weight and computes its column block of the result; the GEMM needs no collective. `value` is the
 whole job's TFLOP/s: 2*M*N*K divided by the slowest rank's time per step.
@@ -346,14 +346,15 @@ def main():
     sync_all()
 
     # Timing rule: a step's inputs must not sit in L2 from the step before. One rank's share of the problem is
-    # 200 MiB at N=1 (larger than the 126 MB L2, streamed anew every step) but 81 MiB at N=8, so for N>1 each
-    # step is timed by its own event pair and a 256 MiB buffer is read between the steps (outside the pairs).
-    flush_between = algo_bytes(n_local) < 2 * 126e6
-    flush_buf = torch.zeros(256 << 20, dtype=torch.uint8, device=dev) if flush_between else None
+    # 200 MiB at N=1 but 81 MiB at N=8, less than the 126 MB L2. So at every N each step is timed by its own pair
+    # of CUDA events on the launching stream and a 256 MiB buffer is read between the steps, outside the pairs
+    # (the read also keeps the GPU busy while the host enqueues the next step, so no launch latency lands inside
+    # a pair). The time of K steps is the sum over the pairs; the K steps are bracketed by barrier + synchronize.
+    flush_buf = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
 
-    def timed(fn, steps):
+    def timed(fn, steps, flush=True):
         sync_all()
-        if not flush_between:
+        if not flush:
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
             for _ in range(steps):
@@ -411,7 +412,7 @@ def main():
     if not args.no_sustained:
         n_long = max(args.steps, int(1200.0 / ms_per_step) + 1)
         with ClockSampler(local_rank, period=0.01) as long_clocks:
-            long_ms = timed(step, n_long)
+            long_ms = timed(step, n_long, flush=False)  # back to back: the GPU never idles, the power cap sets the clock
         long_tf = flops_launch / (long_ms / n_long * 1e-3) / 1e12
         roofline["sustained"] = {
             "achieved": long_tf, "peak": 2.0 * peaks["bf16_sustained"], "unit": "TFLOP/s",
@@ -495,10 +496,8 @@ def main():
         "config": {"workload": WORKLOAD, "global_shape": [M, N, K], "per_gpu_shape": [M, n_local, K],
                    "sharding": f"N-sharded x{world} (each rank its own rows of the [N, K] weight), no collective",
                    "l2": f"operands + outputs = {algo_bytes(n_local) / 2**20:.0f} MiB per step and rank: "
-                         + ("L2 flushed between the timed steps by a 256 MiB read, each step timed by its own pair of "
-                            "CUDA events (sum over the steps, max over ranks)" if flush_between else
-                            "larger than the 126 MB L2, back-to-back steps between one pair of CUDA events (no flush "
-                            "needed)")},
+                         "L2 flushed between the timed steps by a 256 MiB read, each step timed by its own pair of "
+                         "CUDA events (sum over the steps, max over ranks)"},
         "pct_of_nominal_fp8_peak": 100.0 * value / (NOMINAL_FP8_TFLOPS * world),
         "roofline": roofline, "cpu_baseline": cb, "e2e": e2e, "gpu_launches": int(launches),
         "clocks": clocks.summary(), "device_status": status,

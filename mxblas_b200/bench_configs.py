@@ -203,13 +203,10 @@ def dist_main() -> None:
     t_all = timed(True)
     peer = {}
     if world > 1:
-        m = shape[0]
-        auto = dist_mod.peer_row_chunks(m, m // args[2].shape[0], len(args) > 7 and bool(args[7]), False)
         peer["whole_sm"] = timed("peer", peer_chunks=1)
         peer["whole_dma"] = timed("peer", peer_chunks=1, peer_transport="dma")
-        if auto > 1:
-            peer[f"chunks{auto}_sm"] = timed("peer")
-            peer[f"chunks{auto}_dma"] = timed("peer", peer_transport="dma")
+        peer["auto_chunks_sm"] = timed("peer")
+        peer["auto_chunks_dma"] = timed("peer", peer_transport="dma")
     if rank == 0:
         print(json.dumps({"config": a.config, "per_rank_shape": list(shape), "n_gpus": world,
                           "gemm_us": t_gemm * 1e6, "gemm_plus_gather_us": t_all * 1e6,

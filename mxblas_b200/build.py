@@ -33,6 +33,7 @@ SOURCES = [
     "mxb_inst_promote.cu",
     "mxb_inst_mx.cu",
     "mxb_inst_pair.cu",
+    "mxb_inst_quant2d.cu",
 ]
 
 NVCC_FLAGS = [

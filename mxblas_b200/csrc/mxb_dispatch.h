@@ -53,5 +53,7 @@ const KernelEntry* epilogue_kernels(int* count);
 const KernelEntry* promote_kernels(int* count);
 const KernelEntry* mx_kernels(int* count);
 const KernelEntry* pair_kernels(int* count);  // CTA-pair (cta_group::2) kernels, bn == 256
+const KernelEntry* quant2d_kernels(int* count);       // OUT_QUANT_2D, one CTA per tile, all scale modes
+const KernelEntry* quant2d_pair_kernels(int* count);  // OUT_QUANT_2D, CTA pairs
 
 }  // namespace mxb

@@ -136,17 +136,19 @@ static int operand_map(const void* ptr, long long rows, long long k, long long p
 // ---------------------------------------------------------------------------------------------
 static const KernelEntry* find_kernel(int bn, int scale_mode, int out_mode, int epi_warps) {
   int n = 0;
-  const KernelEntry* t = scale_mode == SCALE_EPILOGUE  ? epilogue_kernels(&n)
-                         : scale_mode == SCALE_PROMOTE ? promote_kernels(&n)
-                                                       : mx_kernels(&n);
+  const KernelEntry* t = out_mode == OUT_QUANT_2D      ? quant2d_kernels(&n)
+                         : scale_mode == SCALE_EPILOGUE ? epilogue_kernels(&n)
+                         : scale_mode == SCALE_PROMOTE  ? promote_kernels(&n)
+                                                        : mx_kernels(&n);
   for (int i = 0; i < n; ++i)
-    if (t[i].bn == bn && t[i].out_mode == out_mode && t[i].epi_warps == epi_warps) return &t[i];
+    if (t[i].bn == bn && t[i].scale_mode == scale_mode && t[i].out_mode == out_mode && t[i].epi_warps == epi_warps)
+      return &t[i];
   return nullptr;
 }
 
 static const KernelEntry* find_pair_kernel(int bn, int scale_mode, int out_mode, int epi_warps) {
   int n = 0;
-  const KernelEntry* t = pair_kernels(&n);
+  const KernelEntry* t = out_mode == OUT_QUANT_2D ? quant2d_pair_kernels(&n) : pair_kernels(&n);
   for (int i = 0; i < n; ++i)
     if (t[i].bn == bn && t[i].scale_mode == scale_mode && t[i].out_mode == out_mode && t[i].epi_warps == epi_warps)
       return &t[i];
@@ -172,6 +174,7 @@ struct Plan {
   int swap, bn, scale_mode, out_mode, epi_warps, raster, splits, ctas;
   int pair;   // 1: CTA pairs on 256 x 256 tiles (cta_group::2)
   int tail_first, tail_splits;  // pair kernels: tiles from tail_first on are cut into tail_splits K slices
+  int qx, qy;  // quantisation block in kernel terms (rows of X by rows of Y)
   int probe;  // SCALE_MX behind a device-side power-of-two test, with a SCALE_PROMOTE twin
   const KernelEntry* kernel;
   const KernelEntry* fallback;  // probe only
@@ -194,9 +197,11 @@ static int validate(const mxb_problem_t& q) {
   if (!is_fp8(q.in_dtype) || !is_scale_dt(q.scale_dtype)) return MXB_ERR_INVALID;
   if (q.flags & MXB_OUT_QUANT) {
     if (!is_fp8(q.out_dtype)) return MXB_ERR_INVALID;
-    if (q.qm != 1) return MXB_ERR_UNSUPPORTED;  // the reference too: generator.py:971
+    // [1, QN] groups as in the reference (generator.py:971-974), or two-dimensional [QM, QN] blocks with
+    // QM a power of two up to 128 (the reference refuses those by static_assert)
+    if (q.qm < 1 || q.qm > 128 || (q.qm & (q.qm - 1))) return MXB_ERR_UNSUPPORTED;
     if (q.qn != 16 && q.qn != 32 && q.qn != 64 && q.qn != 128) return MXB_ERR_UNSUPPORTED;
-    if (q.n % q.qn) return MXB_ERR_INVALID;
+    if (q.n % q.qn || q.m % q.qm) return MXB_ERR_INVALID;
   } else if (!is_hp(q.out_dtype)) {
     return MXB_ERR_INVALID;
   }
@@ -226,15 +231,22 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
   // operands (M <= 128: a weight tile then streams through the 128-row axis and M is the narrow tile width).
   // Promotion kernels gain nothing from that (their time is the K loop of a tile, not its width) and run
   // 1.3-1.5x faster unswapped at M = 128.
+  // Two-dimensional quantisation blocks swap only for transposed outputs.
+  const bool q2d = quant && q.qm > 1;
   int swap = cfg && cfg->swap >= 0 ? cfg->swap : -1;
-  if (swap < 0) swap = (out_t || (q.m <= 128 && pl.scale_mode != SCALE_PROMOTE)) ? 1 : 0;
+  if (swap < 0) swap = (out_t || (q.m <= 128 && pl.scale_mode != SCALE_PROMOTE && !q2d)) ? 1 : 0;
   pl.swap = swap;
   pl.rx = swap ? q.n : q.m;
   pl.ry = swap ? q.m : q.n;
 
   pl.probe = pl.scale_mode == SCALE_MX && !(q.flags & MXB_IN_SCALES_POW2);
 
-  pl.out_mode = !quant ? OUT_HP : (swap ? OUT_QUANT_X : OUT_QUANT_Y);
+  pl.out_mode = !quant ? OUT_HP : q2d ? OUT_QUANT_2D : (swap ? OUT_QUANT_X : OUT_QUANT_Y);
+  // a quantisation block in kernel terms: qx rows of X (lanes and warps) by qy rows of Y (registers)
+  pl.qx = !quant ? 0 : (swap ? q.qn : q.qm);
+  pl.qy = !quant ? 0 : (swap ? q.qm : q.qn);
+  if (q2d && (pl.qy < 16 || pl.qx < 2)) return MXB_ERR_UNSUPPORTED;  // e.g. [2, 16] blocks with out_transpose
+  const bool cross_warp_quant = (pl.out_mode == OUT_QUANT_X && q.qn > 32) || (q2d && pl.qx > 32);
 
   // Skinny problems whose 128-row tiles alone cannot occupy the GPU (a decode step against a weight of a few
   // thousand rows): narrow Y tiles on the two-CTA-per-SM kernels and a split K, chosen to bring the number of
@@ -245,7 +257,7 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
   {
     const int x_tiles = (pl.rx + 127) / 128, kblocks = (q.k + 127) / 128;
     const bool free_choice = !(cfg && (cfg->bn > 0 || cfg->splits > 0 || cfg->cta_pair == 2 || cfg->ctas > 0));
-    const bool split_ok = !(pl.out_mode == OUT_QUANT_X && q.qn > 32);
+    const bool split_ok = !cross_warp_quant;
     if (free_choice && swap && pl.scale_mode == SCALE_EPILOGUE && pl.ry <= 128 && x_tiles < sms && split_ok) {
       const int slots = 2 * sms;
       long long best_units = 0;
@@ -280,6 +292,11 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
     }
     if (pl.scale_mode == SCALE_MX && bn > 128)
       bn = (pl.out_mode == OUT_QUANT_Y && q.qn > 32) ? 128 : 224;
+    // two-dimensional blocks exist for 128- and 256-wide tiles (224 on the block-scaled CTA pairs)
+    if (q2d) {
+      if (bn < 128) bn = 128;
+      if (pl.scale_mode == SCALE_MX) bn = 128;
+    }
   }
   pl.bn = bn;
   int ew = cfg && cfg->epi_warps > 0 ? cfg->epi_warps : 0;
@@ -289,6 +306,10 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
     if (pl.scale_mode == SCALE_EPILOGUE && bn == 256 && quant) ew = 8;
     // a quantisation group must stay inside one thread's column slice
     if (pl.out_mode == OUT_QUANT_Y && q.qn > bn / (ew / 4)) ew = 4;
+    if (q2d) {
+      ew = (pl.scale_mode == SCALE_MX) ? 4 : (pl.scale_mode == SCALE_PROMOTE || bn == 256) ? 8 : 4;
+      if (pl.qy > bn / (ew / 4)) ew = 4;
+    }
   }
   pl.epi_warps = ew;
   // CTA pairs: 256 x 256 tiles with scales constant along K, 256 x 224 tiles on the block-scaled MMA;
@@ -297,7 +318,7 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
   const bool no_split = !(cfg && cfg->splits > 1);
   const bool pair_epi = pl.scale_mode == SCALE_EPILOGUE && (bn == 256 || (bn == 224 && ew == 4)) && no_split;
   const bool pair_mx = pl.scale_mode == SCALE_MX && (bn == 224 || !(cfg && cfg->bn > 0)) && no_split &&
-                       !(pl.out_mode == OUT_QUANT_Y && q.qn > 32) && ew == 4;
+                       !(pl.out_mode == OUT_QUANT_Y && q.qn > 32) && !(q2d && pl.qy > 32) && ew == 4;
   // promotion pairs: one scale group per 128-deep K block, eight promotion warps, no cross-lane quantisation
   const bool pair_promote = pl.scale_mode == SCALE_PROMOTE && bn == 256 && ew == 8 && no_split && q.sk == 128 &&
                             pl.out_mode != OUT_QUANT_X;
@@ -316,14 +337,14 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
   pl.kernel = pl.pair ? find_pair_kernel(bn, pl.scale_mode, pl.out_mode, ew)
                       : find_kernel(bn, pl.scale_mode, pl.out_mode, ew);
   if (pl.kernel == nullptr) return MXB_ERR_UNSUPPORTED;
-  if (pl.out_mode == OUT_QUANT_Y) {
+  if (pl.out_mode == OUT_QUANT_Y || q2d) {
     const int cols = bn / (ew / 4);
-    if (cols % q.qn) return MXB_ERR_UNSUPPORTED;
+    if (cols % pl.qy) return MXB_ERR_UNSUPPORTED;
   }
   if (pl.probe) {
     pl.fallback_bn = bn > 128 ? 128 : bn;
     int few = pl.fallback_bn >= 128 ? 8 : 4;
-    if (pl.out_mode == OUT_QUANT_Y && q.qn > pl.fallback_bn / (few / 4)) few = 4;
+    if ((pl.out_mode == OUT_QUANT_Y || q2d) && pl.qy > pl.fallback_bn / (few / 4)) few = 4;
     pl.fallback = find_kernel(pl.fallback_bn, SCALE_PROMOTE, pl.out_mode, few);
     if (pl.fallback == nullptr) return MXB_ERR_UNSUPPORTED;
   }
@@ -342,8 +363,7 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
   int splits = cfg && cfg->splits > 0 ? cfg->splits : skinny_splits;
   // promotion kernels split K only where every slice starts on a scale group (groups of at most one K block)
   // (K slices start on 128-wide K blocks, so a scale group must divide 128: 32, 64 or 128)
-  const bool split_ok = !(pl.scale_mode == SCALE_PROMOTE && (q.sk > 128 || 128 % q.sk != 0)) &&
-                        !(pl.out_mode == OUT_QUANT_X && q.qn > 32);
+  const bool split_ok = !(pl.scale_mode == SCALE_PROMOTE && (q.sk > 128 || 128 % q.sk != 0)) && !cross_warp_quant;
   if (splits == 0) {
     splits = 1;
     // Split-K pays only when the tiles alone cannot occupy the GPU (measured on B200: with 224 tiles on
@@ -581,12 +601,14 @@ static int run_gemm(const mxb_problem_t& q, const mxb_config_t* cfg, const void*
   p.oscale = out_scale;
   if (quant) {
     const bool cs_t = (q.flags & MXB_OUT_SCALE_TRANSPOSE) != 0;
-    // scale (m, g) lives at m*sm_ + g*sg
+    // the scale of row block mb (= m / qm) and column group g lives at mb*sm_ + g*sg
     const long long sm_ = cs_t ? 1 : q.ldcs, sg = cs_t ? q.ldcs : 1;
     p.os_xs = pl.swap ? sg : sm_;
     p.os_ys = pl.swap ? sm_ : sg;
   }
   p.qn = quant ? q.qn : 0;
+  p.qx = pl.qx;
+  p.qy = pl.qy;
   p.pow2_out = (q.flags & MXB_OUT_SCALE_POW2) ? 1 : 0;
   p.fmt_x = q.in_dtype == MXB_E5M2 ? 1 : 0;
   p.fmt_y = p.fmt_x;

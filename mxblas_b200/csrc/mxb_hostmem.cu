@@ -65,9 +65,10 @@ extern "C" int mxb_gemm_host(const mxb_problem_t* problem, const void* left, con
   const bool out_t = (q.flags & MXB_OUT_TRANSPOSE) != 0;
   const bool cs_t = (q.flags & MXB_OUT_SCALE_TRANSPOSE) != 0;
   const int groups = quant ? q.n / q.qn : 0;
+  const int qm = quant && q.qm > 1 ? q.qm : 1;  // rows of the result that share a row of output scales
   if (q.lda != q.k || q.ldb != q.k) return MXB_ERR_UNSUPPORTED;
   if (q.ldc != (out_t ? q.m : q.n)) return MXB_ERR_UNSUPPORTED;
-  if (quant && q.ldcs != (cs_t ? q.m : groups)) return MXB_ERR_UNSUPPORTED;
+  if (quant && q.ldcs != (cs_t ? q.m / qm : groups)) return MXB_ERR_UNSUPPORTED;
 
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev >= 64) return MXB_ERR_CUDA;
@@ -130,7 +131,7 @@ extern "C" int mxb_gemm_host(const mxb_problem_t* problem, const void* left, con
   if (!ensure(d.left, static_cast<size_t>(q.m) * q.k) || !ensure(d.right, static_cast<size_t>(q.n) * q.k) ||
       !ensure(d.out, static_cast<size_t>(q.m) * q.n * esz_out) || !ensure(d.ls, ls_rows * ls_cols * ssz) ||
       !ensure(d.rs, rs_rows * ls_cols * ssz) ||
-      !ensure(d.os, quant ? static_cast<size_t>(q.m) * groups * ssz : 0) || !ensure(d.ws, ws_bytes, d.compute))
+      !ensure(d.os, quant ? static_cast<size_t>(q.m / qm) * groups * ssz : 0) || !ensure(d.ws, ws_bytes, d.compute))
     return MXB_ERR_CUDA;
 
   // every enqueue's return code is kept: the first failure ends the call with MXB_ERR_CUDA after the
@@ -158,7 +159,7 @@ extern "C" int mxb_gemm_host(const mxb_problem_t* problem, const void* left, con
         const size_t ls_off = (row0 / q.sm) * static_cast<size_t>(q.as_rs) * ssz;
         const size_t rs_off = (col0 / q.sn) * static_cast<size_t>(q.bs_rs) * ssz;
         char* out_b = static_cast<char*>(d.out.ptr) + (row0 * q.n + col0) * esz_out;
-        char* os_b = static_cast<char*>(d.os.ptr) + (row0 * groups + (quant ? col0 / q.qn : 0)) * ssz;
+        char* os_b = static_cast<char*>(d.os.ptr) + ((row0 / qm) * groups + (quant ? col0 / q.qn : 0)) * ssz;
         st = mxb_gemm(&sub, static_cast<char*>(d.left.ptr) + row0 * q.k, static_cast<char*>(d.right.ptr) + col0 * q.k,
                       out_b, static_cast<char*>(d.ls.ptr) + ls_off, static_cast<char*>(d.rs.ptr) + rs_off,
                       quant ? os_b : nullptr, ws_bytes ? d.ws.ptr : nullptr, ws_bytes, d.compute);
@@ -172,9 +173,9 @@ extern "C" int mxb_gemm_host(const mxb_problem_t* problem, const void* left, con
         // output scales: rows of a block are only (nb / qn) scales long, too short for efficient DMA, so they
         // go back per row block, whole rows at a time, once the row block's last column block is done
         if (quant && ++cols_done[i] == bn)
-          ck(cudaMemcpyAsync(static_cast<char*>(out_scale) + row0 * groups * ssz,
-                          static_cast<char*>(d.os.ptr) + row0 * groups * ssz, static_cast<size_t>(mb) * groups * ssz,
-                          cudaMemcpyDeviceToHost, d.d2h));
+          ck(cudaMemcpyAsync(static_cast<char*>(out_scale) + (row0 / qm) * groups * ssz,
+                             static_cast<char*>(d.os.ptr) + (row0 / qm) * groups * ssz,
+                             static_cast<size_t>(mb / qm) * groups * ssz, cudaMemcpyDeviceToHost, d.d2h));
       }
   };
   // with out_transpose (or transposed scales) there is one block and the results are copied back whole below
@@ -207,7 +208,8 @@ extern "C" int mxb_gemm_host(const mxb_problem_t* problem, const void* left, con
       ck(cudaStreamWaitEvent(d.d2h, d.gemm_done[0], 0));
       ck(cudaMemcpyAsync(out, d.out.ptr, static_cast<size_t>(q.m) * q.n * esz_out, cudaMemcpyDeviceToHost, d.d2h));
       if (quant)
-        ck(cudaMemcpyAsync(out_scale, d.os.ptr, static_cast<size_t>(q.m) * groups * ssz, cudaMemcpyDeviceToHost, d.d2h));
+        ck(cudaMemcpyAsync(out_scale, d.os.ptr, static_cast<size_t>(q.m / qm) * groups * ssz, cudaMemcpyDeviceToHost,
+                           d.d2h));
     }
   }
   cudaError_t e1 = cudaStreamSynchronize(d.h2d);

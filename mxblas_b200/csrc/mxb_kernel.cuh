@@ -25,7 +25,7 @@
 namespace mxb {
 
 enum : int { SCALE_EPILOGUE = 0, SCALE_PROMOTE = 1, SCALE_MX = 2 };
-enum : int { OUT_HP = 0, OUT_QUANT_Y = 1, OUT_QUANT_X = 2 };
+enum : int { OUT_HP = 0, OUT_QUANT_Y = 1, OUT_QUANT_X = 2, OUT_QUANT_2D = 3 };
 enum : int { DT_FP32 = 0, DT_BF16 = 1, DT_FP16 = 2, DT_E4M3 = 3, DT_E5M2 = 4 };
 
 struct GemmParams {
@@ -49,8 +49,9 @@ struct GemmParams {
   int out_dtype;             // DT_BF16 / DT_FP16 / DT_E4M3 / DT_E5M2
   int vec_ok;                // out_ys == 1 and rows are 16-byte aligned: 16-byte vector stores allowed
   void* oscale;
-  long long os_xs, os_ys;    // QUANT_Y: index (x, y/qn); QUANT_X: index (x/qn, y)
+  long long os_xs, os_ys;    // QUANT_Y: index (x, y/qn); QUANT_X: index (x/qn, y); QUANT_2D: index (x/qx, y/qy)
   int qn;                    // quantisation group length
+  int qx, qy;                // OUT_QUANT_2D: a quantisation block is qx rows of X by qy columns of Y
   int pow2_out;              // round output scales up to a power of two
   int fmt_x, fmt_y;          // 0 = e4m3, 1 = e5m2
   unsigned int* status;      // device status word (0 = ok)
@@ -441,8 +442,102 @@ struct OutputStage {
     return true;
   }
 
+  // ---- two-dimensional quantisation blocks: qx rows (lanes, then warps) by qy columns (registers) ----------
+  // The reference's epilogue refuses them (static_assert(c_q_m == 1), mxblas/gemm/generator.py:971); the
+  // arithmetic per block is the one of its [1, QN] groups with the maximum taken over the whole block.
+  // Two passes over the thread's row slice: pass 1 leaves the maximum of every 16 columns in a register, the
+  // maxima are merged along y up to qy columns and along x over the block's rows (xor butterfly inside the
+  // warp, shared memory and a bounded mbarrier wait across the warps of a 64- or 128-row block); pass 2 fetches
+  // the values again, scales them and stores codes and scales. Returns false if a cross-warp wait was abandoned.
+  template <int SPAN, int NG>
+  __device__ __forceinline__ static void merge_y(float (&g)[NG], int qy) {
+    if constexpr (NG >= SPAN) {
+      if (qy >= 16 * SPAN) {
+#pragma unroll
+        for (int i = 0; i < NG; i += SPAN) {
+          const float m = fmaxf(g[i], g[i + SPAN / 2]);
+#pragma unroll
+          for (int t = 0; t < SPAN; ++t) g[i + t] = m;
+        }
+      }
+    }
+  }
+
+  __device__ __forceinline__ bool run_quant_2d() const {
+    constexpr int NG = Cfg::COLS_PER_THREAD / 16;
+    const int qx = p.qx, qy = p.qy;
+    float g[NG];
+#pragma unroll
+    for (int c = 0; c < Cfg::CHUNKS; ++c) {
+      float v[32];
+      fetch(c, v);
+      float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        a0 = fmaxf(a0, fabsf(v[j]));
+        a1 = fmaxf(a1, fabsf(v[16 + j]));
+      }
+      g[2 * c] = a0;
+      g[2 * c + 1] = a1;
+    }
+    // along y: every 16-column entry ends up holding the maximum of the qy columns of its block
+    merge_y<2>(g, qy);
+    merge_y<4>(g, qy);
+    merge_y<8>(g, qy);
+    // along x inside the warp (rows beyond rx hold zeros and never raise a maximum)
+    for (int off = 1; off < 32 && off < qx; off <<= 1) {
+#pragma unroll
+      for (int i = 0; i < NG; ++i) g[i] = fmaxf(g[i], __shfl_xor_sync(0xffffffffu, g[i], off));
+    }
+    if (qx > 32) {
+      // blocks of 64 or 128 rows span two or four warps: all lanes of a warp now hold the same NG maxima,
+      // lane i publishes entry i
+      const uint32_t ph = *xphase;
+      float* slot = xmax_s + (ph & 1) * 128;
+#pragma unroll
+      for (int i = 0; i < NG; ++i)
+        if (lane == i) slot[quad * 32 + i] = g[i];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(xbar);
+      if (!mbar_wait(xbar, ph & 1, abort_flag, p.status, DEV_TIMEOUT_EPILOGUE)) return false;
+      *xphase = ph + 1;
+      const int qbase = qx == 64 ? (quad & 2) : 0;
+      const int qcnt = qx == 64 ? 2 : 4;
+#pragma unroll
+      for (int i = 0; i < NG; ++i) {
+        float m = slot[qbase * 32 + i];
+        for (int t = 1; t < qcnt; ++t) m = fmaxf(m, slot[(qbase + t) * 32 + i]);
+        g[i] = m;
+      }
+    }
+    const bool writer = xrow < p.rx && (xrow & (qx - 1)) == 0;
+#pragma unroll
+    for (int c = 0; c < Cfg::CHUNKS; ++c) {
+      const float s0 = group_scale(g[2 * c], inv_fp8_max, p.pow2_out);
+      const float s1 = group_scale(g[2 * c + 1], inv_fp8_max, p.pow2_out);
+      const float i0 = 1.0f / s0, i1 = 1.0f / s1;
+      float v[32];
+      fetch(c, v);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        v[j] *= i0;
+        v[16 + j] *= i1;
+      }
+      store_fp8(c, v);
+      const int y0 = ycol0 + c * 32;
+      if (writer) {
+        const long long base = static_cast<long long>(xrow / qx) * p.os_xs;
+        if (y0 < p.ry && (y0 % qy) == 0) store_scale(p.oscale, base + (y0 / qy) * p.os_ys, p.scale_dtype, s0);
+        if (qy == 16 && y0 + 16 < p.ry) store_scale(p.oscale, base + (y0 / 16 + 1) * p.os_ys, p.scale_dtype, s1);
+      }
+    }
+    return true;
+  }
+
   __device__ __forceinline__ bool run() const {
-    if constexpr (Cfg::OUT_MODE == OUT_HP) {
+    if constexpr (Cfg::OUT_MODE == OUT_QUANT_2D) {
+      return run_quant_2d();
+    } else if constexpr (Cfg::OUT_MODE == OUT_HP) {
 #pragma unroll
       for (int c = 0; c < Cfg::CHUNKS; ++c) {
         float v[32];

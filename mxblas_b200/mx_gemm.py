@@ -159,11 +159,13 @@ def get_meta_info(
                 f"that divide m ({m}) and n ({n})."
             )
         qm, qn = int(quant_size[0]), int(quant_size[1])
-        # the reference has templates only for 1 x {16, 32, 64, 128} groups (generator.py:971-974)
-        if qm != 1 or qn not in (16, 32, 64, 128):
+        # The reference has templates only for 1 x {16, 32, 64, 128} groups and refuses QM > 1 when the kernel
+        # is compiled (generator.py:971-974); here QM may also be a power of two up to 128 (two-dimensional
+        # blocks, e.g. [128, 128] or [32, 32]).
+        if qm > 128 or (qm & (qm - 1)) or qn not in (16, 32, 64, 128):
             raise ValueError(
-                f"No matching kernel for quant_size {tuple(quant_size)}: groups must be "
-                "[1, 16], [1, 32], [1, 64] or [1, 128]."
+                f"No matching kernel for quant_size {tuple(quant_size)}: blocks must be [QM, QN] with QN in "
+                "(16, 32, 64, 128) and QM a power of two up to 128."
             )
     else:
         qm, qn = 0, 0  # a quant_size passed without output_quant is accepted and ignored
@@ -268,8 +270,11 @@ def mx_gemm_kernel(
     ``right_scale`` [K/SK, N/SN] in fp16/bf16/fp32. Returns ``(C, C_scale)``; ``C_scale`` has the
     dtype of the input scales and is a 0-dim empty tensor when ``output_quant`` is False.
 
+    ``quant_size`` [QM, QN]: QM = 1 as in the reference, or a power of two up to 128 for two-dimensional
+    blocks (``C_scale`` is then [M/QM, N/QN]).
+
     ``out_transpose=True`` returns C^T as a contiguous [N, M] tensor and ``out_scale_transpose=True``
-    returns C_scale^T as a contiguous [N/QN, M] tensor (the reference declares both flags but has
+    returns C_scale^T as a contiguous [N/QN, M/QM] tensor (the reference declares both flags but has
     no kernel for them: mxblas/gemm/generator.py:933-936, mxblas/gemm/template.py:74).
     """
     if not left.is_cuda:
@@ -292,8 +297,8 @@ def mx_gemm_kernel(
         # outputs (mx_gemm.py:301-325)
         out = torch.empty((n, m) if meta.out_transpose else (m, n), dtype=meta.out_dtype, device=dev)
         if meta.quant:
-            g = n // meta.qn
-            out_scale = torch.empty((g, m) if meta.out_scale_transpose else (m, g), dtype=meta.scale_dtype,
+            g, mb = n // meta.qn, m // meta.qm
+            out_scale = torch.empty((g, mb) if meta.out_scale_transpose else (mb, g), dtype=meta.scale_dtype,
                                     device=dev)
             ldcs = out_scale.stride(0)
         else:

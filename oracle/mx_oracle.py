@@ -63,13 +63,16 @@ def pow2_ceil(s: torch.Tensor) -> torch.Tensor:
 
 def quantize_groups(
     c32: torch.Tensor, qn: int, scale_dtype: torch.dtype, out_dtype: torch.dtype = torch.float8_e4m3fn,
-    pow2: bool = False,
+    pow2: bool = False, qm: int = 1,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:  # fmt: skip
-    """Step 4 above. Returns (codes [M, N] fp8, scales [M, N/qn] in scale_dtype, s32 [M, N/qn])."""
+    """Step 4 above. Returns (codes [M, N] fp8, scales [M/qm, N/qn] in scale_dtype, s32 [M/qm, N/qn]).
+
+    ``qm`` > 1 (an extension: the reference's epilogue asserts qm == 1, generator.py:971) takes the maximum
+    over a [qm, qn] block instead of a [1, qn] group; everything else is the same arithmetic."""
     m, n = c32.shape
-    assert n % qn == 0
-    g = c32.reshape(m, n // qn, qn)
-    amax = g.abs().amax(dim=2).clamp_min(SCALE_MIN_THRES)
+    assert n % qn == 0 and m % qm == 0
+    g = c32.reshape(m // qm, qm, n // qn, qn)
+    amax = g.abs().amax(dim=(1, 3)).clamp_min(SCALE_MIN_THRES)
     inv_max = torch.tensor(1.0 / FP8_MAX[out_dtype], dtype=torch.float32)
     s32 = amax * inv_max
     if pow2:
@@ -78,7 +81,7 @@ def quantize_groups(
     fmax = FP8_MAX[out_dtype]
     # torch's CPU cast to fp8 rounds to nearest even but does not saturate: clamp first, which is
     # what __NV_SATFINITE does in the kernel (and what mxblas/utils.py:85 does for the same reason)
-    codes = (g * inv.unsqueeze(2)).clamp(-fmax, fmax).reshape(m, n).to(out_dtype)
+    codes = (g * inv[:, None, :, None]).clamp(-fmax, fmax).reshape(m, n).to(out_dtype)
     return codes, s32.to(scale_dtype), s32
 
 
@@ -115,9 +118,10 @@ def mx_gemm(
     c32 = mx_gemm_c32(left, right, left_scale, right_scale)
     scale_dtype = left_scale.dtype
     if output_quant:
-        assert quant_size is not None and quant_size[0] == 1
+        assert quant_size is not None
         out_dtype = out_dtype or left.dtype
-        out, out_scale, _ = quantize_groups(c32, int(quant_size[1]), scale_dtype, out_dtype, out_scale_pow2)
+        out, out_scale, _ = quantize_groups(c32, int(quant_size[1]), scale_dtype, out_dtype, out_scale_pow2,
+                                            int(quant_size[0]))
     else:
         out = c32.to(out_dtype or torch.bfloat16)
         out_scale = torch.empty([], dtype=scale_dtype)

@@ -66,8 +66,11 @@ def test_unsupported_layouts_and_alignment_raise_value_error():
     with pytest.raises(ValueError):
         get_meta_info(e4, e4, f32, f32, False, None, None, (64, 24), (24, 64), (1, 1), (1, 1), (24, 1), (1, 24),
                       (1, 1), (1, 1), False, False)
-    # quantisation groups the reference has no template for (generator.py:971-974)
-    for qs in ((2, 16), (1, 8), (1, 256)):
+    # quantisation groups neither the reference (generator.py:971-974) nor this library has a kernel for;
+    # QM > 1 as a power of two up to 128 is an extension here and passes
+    get_meta_info(e4, e4, f32, f32, True, (2, 16), None, (64, 64), (64, 64), (1, 1), (1, 1), (64, 1), (1, 64),
+                  (1, 1), (1, 1), False, False)
+    for qs in ((3, 16), (1, 8), (1, 256)):
         with pytest.raises(ValueError):
             get_meta_info(e4, e4, f32, f32, True, qs, None, (256, 256), (256, 256), (1, 1), (1, 1), (256, 1),
                           (1, 256), (1, 1), (1, 1), False, False)
@@ -166,8 +169,12 @@ def test_c_abi_rejects_bad_problems_with_status_codes():
     assert _ext.lib.mxb_query_workspace(ctypes.byref(p), None, ctypes.byref(nbytes)) in (
         _ext.MXB_ERR_INVALID, _ext.MXB_ERR_UNSUPPORTED)
     p = _problem(256, 256, 256, 256, 256, 256, True, 16)
-    p.qm = 2
+    p.qm = 3  # rows of a quantisation block: powers of two up to 128
     assert _ext.lib.mxb_query_workspace(ctypes.byref(p), None, ctypes.byref(nbytes)) == _ext.MXB_ERR_UNSUPPORTED
+    p.qm = 256
+    assert _ext.lib.mxb_query_workspace(ctypes.byref(p), None, ctypes.byref(nbytes)) == _ext.MXB_ERR_UNSUPPORTED
+    p.qm = 32
+    assert _ext.lib.mxb_query_workspace(ctypes.byref(p), None, ctypes.byref(nbytes)) == _ext.MXB_OK
     assert _ext.lib.mxb_query_workspace(None, None, ctypes.byref(nbytes)) == _ext.MXB_ERR_INVALID
     # null tensors are refused before any CUDA call
     p = _problem(256, 256, 256, 256, 256, 256)

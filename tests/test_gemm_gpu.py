@@ -32,14 +32,14 @@ def dev():
 
 
 def run_case(left, right_phys, ls, rs, quant=False, qn=16, out_dtype=None, out_t=False, cs_t=False,
-             out_pow2=False, pow2_scales=False, config=None, ls_col_major=False):
+             out_pow2=False, pow2_scales=False, config=None, ls_col_major=False, qm=1):
     """Run the operator on the GPU and the oracle on the CPU; assert the tolerances."""
     d = dev()
     lsd = ls.to(d)
     if ls_col_major:
         lsd = ls.t().contiguous().to(d).t()
     out, osc = mxblas.mx_gemm_kernel(
-        left.to(d), right_phys.to(d).t(), lsd, rs.to(d).t(), quant, torch.Size((1, qn)), out_dtype, out_t, cs_t,
+        left.to(d), right_phys.to(d).t(), lsd, rs.to(d).t(), quant, torch.Size((qm, qn)), out_dtype, out_t, cs_t,
         out_scale_pow2=out_pow2, pow2_scales=pow2_scales, config=config,
     )  # fmt: skip
     assert _ext.device_status() == 0, "a kernel recorded a device-side error"
@@ -55,8 +55,8 @@ def run_case(left, right_phys, ls, rs, quant=False, qn=16, out_dtype=None, out_t
         return met
     fp8 = out_dtype or left.dtype
     assert out.dtype == fp8 and osc.dtype == ls.dtype
-    assert tuple(osc.shape) == ((n // qn, m) if cs_t else (m, n // qn)) and osc.is_contiguous()
-    codes, scales, s32 = orc.quantize_groups(c32, qn, ls.dtype, fp8, out_pow2)
+    assert tuple(osc.shape) == ((n // qn, m // qm) if cs_t else (m // qm, n // qn)) and osc.is_contiguous()
+    codes, scales, s32 = orc.quantize_groups(c32, qn, ls.dtype, fp8, out_pow2, qm)
     gsc = (osc.t() if cs_t else osc).cpu()
     dist = orc.fp8_code_distance(got.contiguous(), codes)
     same = float((dist == 0).float().mean())
@@ -187,6 +187,38 @@ def test_promote_wide_tiles(qn):
     ins = make_inputs(2048, 2560, 256, 1, 128, 128, seed=80 + qn, scale_range=(1e-2, 1.0))
     run_case(*ins, quant=qn > 0, qn=qn or 16)
     run_case(*ins, quant=qn > 0, qn=qn or 16, config=MxbConfig(256, 0, 8, 4, 1, 0))
+
+
+# ---------------------------------------------------------------------------------------------
+# two-dimensional quantisation blocks [QM, QN] with QM > 1 (the reference asserts QM == 1)
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("qm,qn", [(128, 128), (32, 32), (16, 16), (64, 32), (2, 16), (128, 16), (8, 128)])
+@pytest.mark.parametrize("pattern", ["TT", "GB", "GG32"])
+def test_quant_blocks_2d(pattern, qm, qn):
+    m, n, k = 256, 512, 512
+    sm, sn, sk = PATTERNS[pattern](m, n, k)
+    ins = make_inputs(m, n, k, sm, sn, sk, seed=qm * 1000 + qn, pow2=pattern == "GG32")
+    kw = dict(pow2_scales=True) if pattern == "GG32" else {}
+    run_case(*ins, quant=True, qn=qn, qm=qm, **kw)
+    run_case(*ins, quant=True, qn=qn, qm=qm, out_pow2=True, **kw)
+    if qm >= 16:  # transposed outputs put QM on the register axis, which holds blocks of 16 columns or more
+        run_case(*ins, quant=True, qn=qn, qm=qm, out_t=True, cs_t=True, **kw)
+    else:
+        with pytest.raises(ValueError):
+            run_case(*ins, quant=True, qn=qn, qm=qm, out_t=True, **kw)
+
+
+def test_quant_blocks_2d_large_tiles_and_pairs():
+    """256-wide tiles, CTA pairs (default plan of a large problem), ragged tile edges, split K, bf16 scales."""
+    run_case(*make_inputs(4096, 2560, 256, 1, 1, 256, seed=301), quant=True, qn=128, qm=128)       # pairs
+    run_case(*make_inputs(4096, 2560, 384, 1, 128, 128, seed=302), quant=True, qn=32, qm=32)      # promotion pairs
+    run_case(*make_inputs(4096, 4096, 256, 1, 1, 32, seed=303, pow2=True), quant=True, qn=32, qm=32,
+             pow2_scales=True)                                                                     # block-scaled pairs
+    run_case(*make_inputs(1152, 1280, 384, 1, 1, 384, torch.bfloat16, seed=304), quant=True, qn=64, qm=64)
+    run_case(*make_inputs(320, 1088, 272, 1, 1, 272, seed=305), quant=True, qn=16, qm=32)          # ragged tiles
+    run_case(*make_inputs(64, 1024, 4096, 1, 1, 4096, seed=306), quant=True, qn=32, qm=16)         # few tiles
+    run_case(*make_inputs(2560, 3840, 2048, 1, 1, 2048, seed=307), quant=True, qn=32, qm=32)       # K-sliced last wave
+    run_case(*make_inputs(4096, 2560, 256, 1, 1, 256, seed=308), quant=True, qn=32, qm=128, out_t=True, cs_t=True)
 
 
 def test_mx_native_and_fallback_agree():
