@@ -49,12 +49,18 @@ typedef enum mxb_dtype {
 #define MXB_IN_SCALES_POW2 0x10u      /* caller asserts that all input scales are powers of two */
 #define MXB_IN_SCALES_PROBE 0x20u     /* test for power-of-two input scales on the device and use
                                          the native block-scaled MMA when they all are */
+#define MXB_LEFT_COL_MAJOR 0x40u      /* left [M, K] is stored column-major: physically [K, M], row pitch lda */
+#define MXB_RIGHT_ROW_MAJOR 0x80u     /* right [K, N] is stored row-major: physically [K, N], row pitch ldb */
 
 /* One GEMM problem: the fields of the reference's MXGEMMDescriptor
  * (mxblas/gemm/descriptor.py:84-220) plus the strides that the reference reads from the tensors
  * (mxblas/jit_kernels/mx_gemm.py:160-168).
- *   left        [M, K]  fp8, row-major, row pitch lda (elements)
- *   right       [K, N]  fp8, column-major view: physically [N, K] with row pitch ldb
+ *   left        [M, K]  fp8, row-major, row pitch lda (elements); with MXB_LEFT_COL_MAJOR physically [K, M]
+ *   right       [K, N]  fp8, column-major view: physically [N, K] with row pitch ldb; with
+ *                       MXB_RIGHT_ROW_MAJOR physically [K, N]
+ *                       (the reference matches only row-major left x column-major right,
+ *                       mxblas/gemm/template.py:70-73; the other three combinations are the operand layouts
+ *                       of a backward pass: dX = dY . W with W as stored, dW = dY^T . X)
  *   left_scale  [M/sm, K/sk]  element (i, j) at  i*as_rs + j*as_ks
  *   right_scale [K/sk, N/sn]  element (j, i) at  i*bs_rs + j*bs_ks  (i = column block of N)
  *   out         [M, N] row pitch ldc, or with MXB_OUT_TRANSPOSE [N, M] row pitch ldc
@@ -112,6 +118,21 @@ int mxb_gemm(const mxb_problem_t* problem, const void* left, const void* right, 
 int mxb_gemm_cfg(const mxb_problem_t* problem, const mxb_config_t* cfg, const void* left,
                  const void* right, void* out, const void* left_scale, const void* right_scale,
                  void* out_scale, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Grouped GEMM, the expert layers of a mixture-of-experts model: `groups` weight matrices of one shape,
+ * right = [groups][N, K] stacked densely (group stride N * ldb) with right_scale = [groups][N/sn, K/sk] stacked the
+ * same way; the rows of left [M, K] are sorted by group and padded so that every block of `block_rows` (128 or
+ * 256) rows belongs to one group. group_of_block (device memory, M / block_rows ints) names the group of each block;
+ * a negative entry skips the block (its rows of out are left untouched). Row r of out is
+ * left[r] x right[group of r's block]; scaling, output quantisation and flags as for mxb_gemm, except that
+ * MXB_OUT_TRANSPOSE and a row-major right are not supported. block_rows = 256 lets large problems run on CTA
+ * pairs. The reference is a single dense GEMM (mxblas/jit_kernels/mx_gemm.py:340-425) and has no counterpart.
+ * problem->m is the total number of rows, problem->n the columns of ONE group's weight. */
+int mxb_grouped_gemm(const mxb_problem_t* problem, const mxb_config_t* cfg, int groups, const int* group_of_block,
+                     int block_rows, const void* left, const void* right, void* out, const void* left_scale,
+                     const void* right_scale, void* out_scale, void* workspace, size_t workspace_bytes, void* stream);
+int mxb_grouped_query_workspace(const mxb_problem_t* problem, const mxb_config_t* cfg, int groups, int block_rows,
+                                size_t* bytes);
 
 /* Host-memory variant: every tensor pointer is HOST memory (pinned memory makes the copies
  * asynchronous). Copies the operands to device staging buffers owned by the library, runs the

@@ -18,4 +18,6 @@ from .mx_gemm import (  # noqa: F401
     reset_workspaces,
 )
 
-__all__ = ["mx_gemm_kernel", "register_all_kernels", "MxbConfig"]
+from .grouped import mx_grouped_gemm  # noqa: F401,E402
+
+__all__ = ["mx_gemm_kernel", "mx_grouped_gemm", "register_all_kernels", "MxbConfig"]

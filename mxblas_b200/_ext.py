@@ -31,6 +31,8 @@ MXB_OUT_SCALE_TRANSPOSE = 0x4
 MXB_OUT_SCALE_POW2 = 0x8
 MXB_IN_SCALES_POW2 = 0x10
 MXB_IN_SCALES_PROBE = 0x20
+MXB_LEFT_COL_MAJOR = 0x40
+MXB_RIGHT_ROW_MAJOR = 0x80
 
 MXB_STATIC_SCRATCH_BYTES = 8 << 20  # scratch built into the library (mxb_gemm_static_scratch)
 
@@ -43,6 +45,8 @@ EXPORTED_SYMBOLS = (
     "mxb_default_config",
     "mxb_gemm",
     "mxb_gemm_cfg",
+    "mxb_grouped_gemm",
+    "mxb_grouped_query_workspace",
     "mxb_push_block",
     "mxb_push_block_ex",
     "mxb_push_block_dma",
@@ -119,6 +123,10 @@ def _load() -> ctypes.CDLL:
     lib.mxb_gemm.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, sz, vp]
     lib.mxb_gemm_cfg.restype = ctypes.c_int
     lib.mxb_gemm_cfg.argtypes = [pp, cp, vp, vp, vp, vp, vp, vp, vp, sz, vp]
+    lib.mxb_grouped_gemm.restype = ctypes.c_int
+    lib.mxb_grouped_gemm.argtypes = [pp, cp, ctypes.c_int, vp, ctypes.c_int, vp, vp, vp, vp, vp, vp, vp, sz, vp]
+    lib.mxb_grouped_query_workspace.restype = ctypes.c_int
+    lib.mxb_grouped_query_workspace.argtypes = [pp, cp, ctypes.c_int, ctypes.c_int, ctypes.POINTER(sz)]
     lib.mxb_push_block.restype = ctypes.c_int
     lib.mxb_push_block.argtypes = [vp, ctypes.c_longlong, ctypes.POINTER(vp), ctypes.c_int, ctypes.c_longlong,
                                    ctypes.c_longlong, ctypes.c_longlong, vp]

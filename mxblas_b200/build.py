@@ -34,6 +34,8 @@ SOURCES = [
     "mxb_inst_mx.cu",
     "mxb_inst_pair.cu",
     "mxb_inst_quant2d.cu",
+    "mxb_inst_general.cu",
+    "mxb_inst_general_pair.cu",
 ]
 
 NVCC_FLAGS = [

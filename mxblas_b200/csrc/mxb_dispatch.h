@@ -23,6 +23,8 @@ struct KernelEntry {
   int smem_bytes;
   int stages;
   int ctas_per_sm;
+  int two_per_sm;  // 128-wide tile built as a light CTA (two per SM); narrower tiles are light anyway
+  int general;     // also handles operands stored along their rows and grouped GEMMs
 };
 
 template <class Cfg>
@@ -45,7 +47,18 @@ cudaError_t launch_kernel(const LaunchArgs& a) {
 #define MXB_ENTRY(BN, SM, OM, EW)                                                              \
   {                                                                                            \
     BN, SM, OM, EW, &launch_kernel<KernelCfg<BN, SM, OM, EW>>, KernelCfg<BN, SM, OM, EW>::SMEM_BYTES, \
-        KernelCfg<BN, SM, OM, EW>::STAGES, KernelCfg<BN, SM, OM, EW>::CTAS_PER_SM                \
+        KernelCfg<BN, SM, OM, EW>::STAGES, KernelCfg<BN, SM, OM, EW>::CTAS_PER_SM, 0, 0          \
+  }
+#define MXB_ENTRY_GENERAL(BN, SM, OM, EW)                                                                      \
+  {                                                                                                            \
+    BN, SM, OM, EW, &launch_kernel<KernelCfg<BN, SM, OM, EW, false, true>>,                                    \
+        KernelCfg<BN, SM, OM, EW, false, true>::SMEM_BYTES, KernelCfg<BN, SM, OM, EW, false, true>::STAGES,    \
+        KernelCfg<BN, SM, OM, EW, false, true>::CTAS_PER_SM, 0, 1                                              \
+  }
+#define MXB_ENTRY_TWO_PER_SM(BN, SM, OM, EW)                                                                 \
+  {                                                                                                          \
+    BN, SM, OM, EW, &launch_kernel<KernelCfg<BN, SM, OM, EW, true>>, KernelCfg<BN, SM, OM, EW, true>::SMEM_BYTES, \
+        KernelCfg<BN, SM, OM, EW, true>::STAGES, KernelCfg<BN, SM, OM, EW, true>::CTAS_PER_SM, 1, 0          \
   }
 
 // one table per translation unit
@@ -55,5 +68,7 @@ const KernelEntry* mx_kernels(int* count);
 const KernelEntry* pair_kernels(int* count);  // CTA-pair (cta_group::2) kernels, bn == 256
 const KernelEntry* quant2d_kernels(int* count);       // OUT_QUANT_2D, one CTA per tile, all scale modes
 const KernelEntry* quant2d_pair_kernels(int* count);  // OUT_QUANT_2D, CTA pairs
+const KernelEntry* general_kernels(int* count);       // GENERAL instantiations, one CTA per tile
+const KernelEntry* general_pair_kernels(int* count);  // GENERAL instantiations, CTA pairs
 
 }  // namespace mxb

@@ -10,6 +10,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <atomic>
@@ -76,7 +77,7 @@ static encode_tiled_fn get_encode_fn() {
 struct MapKey {
   const void* ptr;
   long long rows, k, pitch;
-  int box_rows;
+  int box_rows;  // -1: operand stored along its rows ([K, rows]), box of 128 rows x 128 K
   bool operator==(const MapKey& o) const {
     return ptr == o.ptr && rows == o.rows && k == o.k && pitch == o.pitch && box_rows == o.box_rows;
   }
@@ -92,11 +93,13 @@ struct MapKeyHash {
   }
 };
 
-// [rows, k] fp8 matrix, row pitch `pitch` bytes; box = box_rows x 128 bytes, 128-byte swizzle.
+// [rows, k] fp8 matrix, row pitch `pitch` bytes; box = box_rows x 128 bytes, 128-byte swizzle. With
+// mn_major the matrix is stored as [k, rows] (pitch between K rows) and a box is 128 K rows of 128 bytes.
 // The reference encodes its maps on every call (mxblas/gemm/generator.py:1276-1278); here they are
 // cached by (pointer, shape).
 static int operand_map(const void* ptr, long long rows, long long k, long long pitch, int box_rows,
-                       CUtensorMap* out) {
+                       CUtensorMap* out, bool mn_major = false) {
+  if (mn_major) box_rows = -1;
   static std::mutex mu;
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   MapKey key{ptr, rows, k, pitch, box_rows};
@@ -113,9 +116,9 @@ static int operand_map(const void* ptr, long long rows, long long k, long long p
     snprintf(g_cuda_error, sizeof(g_cuda_error), "cuTensorMapEncodeTiled entry point not found");
     return MXB_ERR_CUDA;
   }
-  cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(mn_major ? rows : k), static_cast<cuuint64_t>(mn_major ? k : rows)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch)};
-  cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(mn_major ? 128 : box_rows)};
   cuuint32_t estr[2] = {1u, 1u};
   CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -134,21 +137,26 @@ static int operand_map(const void* ptr, long long rows, long long k, long long p
 // ---------------------------------------------------------------------------------------------
 // kernel table
 // ---------------------------------------------------------------------------------------------
-static const KernelEntry* find_kernel(int bn, int scale_mode, int out_mode, int epi_warps) {
+static const KernelEntry* find_kernel(int bn, int scale_mode, int out_mode, int epi_warps, int two_per_sm = 0,
+                                      int general = 0) {
   int n = 0;
-  const KernelEntry* t = out_mode == OUT_QUANT_2D      ? quant2d_kernels(&n)
+  const KernelEntry* t = general                       ? general_kernels(&n)
+                         : out_mode == OUT_QUANT_2D    ? quant2d_kernels(&n)
                          : scale_mode == SCALE_EPILOGUE ? epilogue_kernels(&n)
                          : scale_mode == SCALE_PROMOTE  ? promote_kernels(&n)
                                                         : mx_kernels(&n);
   for (int i = 0; i < n; ++i)
-    if (t[i].bn == bn && t[i].scale_mode == scale_mode && t[i].out_mode == out_mode && t[i].epi_warps == epi_warps)
+    if (t[i].bn == bn && t[i].scale_mode == scale_mode && t[i].out_mode == out_mode && t[i].epi_warps == epi_warps &&
+        t[i].two_per_sm == two_per_sm)
       return &t[i];
   return nullptr;
 }
 
-static const KernelEntry* find_pair_kernel(int bn, int scale_mode, int out_mode, int epi_warps) {
+static const KernelEntry* find_pair_kernel(int bn, int scale_mode, int out_mode, int epi_warps, int general = 0) {
   int n = 0;
-  const KernelEntry* t = out_mode == OUT_QUANT_2D ? quant2d_pair_kernels(&n) : pair_kernels(&n);
+  const KernelEntry* t = general                    ? general_pair_kernels(&n)
+                         : out_mode == OUT_QUANT_2D ? quant2d_pair_kernels(&n)
+                                                    : pair_kernels(&n);
   for (int i = 0; i < n; ++i)
     if (t[i].bn == bn && t[i].scale_mode == scale_mode && t[i].out_mode == out_mode && t[i].epi_warps == epi_warps)
       return &t[i];
@@ -175,6 +183,7 @@ struct Plan {
   int pair;   // 1: CTA pairs on 256 x 256 tiles (cta_group::2)
   int tail_first, tail_splits;  // pair kernels: tiles from tail_first on are cut into tail_splits K slices
   int qx, qy;  // quantisation block in kernel terms (rows of X by rows of Y)
+  int x_mn, y_mn;  // operand stored along its rows instead of along K
   int probe;  // SCALE_MX behind a device-side power-of-two test, with a SCALE_PROMOTE twin
   const KernelEntry* kernel;
   const KernelEntry* fallback;  // probe only
@@ -206,14 +215,34 @@ static int validate(const mxb_problem_t& q) {
     return MXB_ERR_INVALID;
   }
   // TMA: 16-byte aligned row pitches
-  if (q.k % 16 || q.lda % 16 || q.ldb % 16 || q.lda < q.k || q.ldb < q.k) return MXB_ERR_INVALID;
+  const bool left_cm = (q.flags & MXB_LEFT_COL_MAJOR) != 0, right_rm = (q.flags & MXB_RIGHT_ROW_MAJOR) != 0;
+  if (q.lda % 16 || q.ldb % 16) return MXB_ERR_INVALID;
+  if (q.lda < (left_cm ? q.m : q.k) || q.ldb < (right_rm ? q.n : q.k)) return MXB_ERR_INVALID;
+  if (!(left_cm && right_rm) && q.k % 16) return MXB_ERR_INVALID;
   if (q.sk != q.k && q.sk % 32) return MXB_ERR_UNSUPPORTED;
   return MXB_OK;
 }
 
+// MXBLAS_B200_LIGHT128 = 0 / 1 forces the two-CTAs-per-SM form of 128-wide tiles off / on (measurement aid)
+static int light128_override() {
+  static int v = -2;
+  if (v == -2) {
+    const char* e = getenv("MXBLAS_B200_LIGHT128");
+    v = e == nullptr ? -1 : (e[0] == '1' ? 1 : 0);
+  }
+  return v;
+}
+
 static int pick_bn(int ry) { return ry <= 32 ? 32 : ry <= 64 ? 64 : ry <= 128 ? 128 : 256; }
 
-static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl) {
+// A grouped GEMM (one [N, K] weight per group, rows of `left` sorted by group): which group every block of
+// `block_rows` rows of left belongs to (device array, -1 = skip the block), and how many groups there are.
+struct GroupArgs {
+  const int* group_of_block;
+  int groups, block_rows;
+};
+
+static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl, const GroupArgs* grp = nullptr) {
   int st = validate(q);
   if (st != MXB_OK) return st;
   memset(&pl, 0, sizeof(pl));
@@ -234,12 +263,36 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
   // Two-dimensional quantisation blocks swap only for transposed outputs.
   const bool q2d = quant && q.qm > 1;
   int swap = cfg && cfg->swap >= 0 ? cfg->swap : -1;
-  if (swap < 0) swap = (out_t || (q.m <= 128 && pl.scale_mode != SCALE_PROMOTE && !q2d)) ? 1 : 0;
+  if (swap < 0) {
+    swap = (out_t || (q.m <= 128 && pl.scale_mode != SCALE_PROMOTE && !q2d)) ? 1 : 0;
+    // 64 < M <= 128 against a weight whose 256-row tiles nearly fill the GPU in ONE round (28672 rows: 112
+    // tiles on 148 SMs): left stays on the 128-row axis and every CTA streams one 256-row tile of the weight.
+    // Measured on B200, M = 128, N = 28672, K = 8192: 51 us against 55 us swapped on two light CTAs per SM.
+    const long long tiles256 = (static_cast<long long>(q.n) + 255) / 256;
+    if (swap && !out_t && q.m > 64 && pl.scale_mode == SCALE_EPILOGUE && !(q.flags & MXB_RIGHT_ROW_MAJOR) &&
+        tiles256 <= sms && 10 * tiles256 >= 6 * sms)
+      swap = 0;
+  }
+  if (grp != nullptr) {
+    // grouped: left rides the 128-row axis (its row blocks select the weight), result row-major
+    if (out_t || (cfg && cfg->swap == 1) || (cfg && cfg->splits > 1)) return MXB_ERR_UNSUPPORTED;
+    if (grp->groups <= 0 || (grp->block_rows != 128 && grp->block_rows != 256) || q.m % grp->block_rows)
+      return MXB_ERR_INVALID;
+    if (q.sm != 1 && q.sm != q.m && grp->block_rows % q.sm) return MXB_ERR_UNSUPPORTED;
+    swap = 0;
+  }
   pl.swap = swap;
   pl.rx = swap ? q.n : q.m;
   pl.ry = swap ? q.m : q.n;
 
   pl.probe = pl.scale_mode == SCALE_MX && !(q.flags & MXB_IN_SCALES_POW2);
+  // operands stored along their rows (column-major left, row-major right) are staged as 128 x 128 boxes
+  pl.x_mn = swap ? ((q.flags & MXB_RIGHT_ROW_MAJOR) != 0) : ((q.flags & MXB_LEFT_COL_MAJOR) != 0);
+  pl.y_mn = swap ? ((q.flags & MXB_LEFT_COL_MAJOR) != 0) : ((q.flags & MXB_RIGHT_ROW_MAJOR) != 0);
+  // such operands and grouped GEMMs run on the GENERAL kernel instantiations: 128- and 256-wide tiles,
+  // [1, QN] quantisation groups
+  const bool general = pl.x_mn || pl.y_mn || grp != nullptr;
+  if (general && q2d) return MXB_ERR_UNSUPPORTED;
 
   pl.out_mode = !quant ? OUT_HP : q2d ? OUT_QUANT_2D : (swap ? OUT_QUANT_X : OUT_QUANT_Y);
   // a quantisation block in kernel terms: qx rows of X (lanes and warps) by qy rows of Y (registers)
@@ -256,9 +309,9 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
   int skinny_bn = 0, skinny_splits = 0;
   {
     const int x_tiles = (pl.rx + 127) / 128, kblocks = (q.k + 127) / 128;
-    const bool free_choice = !(cfg && (cfg->bn > 0 || cfg->splits > 0 || cfg->cta_pair == 2 || cfg->ctas > 0));
+    const bool free_choice = !(cfg && (cfg->bn > 0 || cfg->splits > 0 || cfg->cta_pair == 2 || cfg->ctas > 0)) && !general;
     const bool split_ok = !cross_warp_quant;
-    if (free_choice && swap && pl.scale_mode == SCALE_EPILOGUE && pl.ry <= 128 && x_tiles < sms && split_ok) {
+    if (free_choice && swap && pl.scale_mode == SCALE_EPILOGUE && pl.ry <= 128 && x_tiles < sms && split_ok && !grp) {
       const int slots = 2 * sms;
       long long best_units = 0;
       for (int bn_try = 64; bn_try >= 32; bn_try /= 2) {
@@ -297,7 +350,16 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
       if (bn < 128) bn = 128;
       if (pl.scale_mode == SCALE_MX) bn = 128;
     }
+    // GENERAL kernels: whole 128-row boxes of an operand stored along its rows
+    if (general) {
+      if (bn < 128) bn = 128;
+      if (bn == 224) bn = 128;
+    }
+    // grouped: a tile of Y must not straddle two groups' matrices, the width divides N
+    if (grp != nullptr) bn = (q.n % 256 == 0 && bn >= 256) ? 256 : 128;
   }
+  if (general && bn != 128 && bn != 256) return MXB_ERR_UNSUPPORTED;
+  if (grp != nullptr && q.n % bn) return MXB_ERR_UNSUPPORTED;
   pl.bn = bn;
   int ew = cfg && cfg->epi_warps > 0 ? cfg->epi_warps : 0;
   if (ew == 0) {
@@ -316,26 +378,39 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
   // no split-K
   const int want_pair = cfg ? cfg->cta_pair : 0;
   const bool no_split = !(cfg && cfg->splits > 1);
-  const bool pair_epi = pl.scale_mode == SCALE_EPILOGUE && (bn == 256 || (bn == 224 && ew == 4)) && no_split;
-  const bool pair_mx = pl.scale_mode == SCALE_MX && (bn == 224 || !(cfg && cfg->bn > 0)) && no_split &&
+  const bool pair_epi = pl.scale_mode == SCALE_EPILOGUE && (bn == 256 || (bn == 224 && ew == 4 && !general)) && no_split;
+  const bool pair_mx = pl.scale_mode == SCALE_MX && !general && (bn == 224 || !(cfg && cfg->bn > 0)) && no_split &&
                        !(pl.out_mode == OUT_QUANT_Y && q.qn > 32) && !(q2d && pl.qy > 32) && ew == 4;
   // promotion pairs: one scale group per 128-deep K block, eight promotion warps, no cross-lane quantisation
-  const bool pair_promote = pl.scale_mode == SCALE_PROMOTE && bn == 256 && ew == 8 && no_split && q.sk == 128 &&
-                            pl.out_mode != OUT_QUANT_X;
+  const bool pair_promote = pl.scale_mode == SCALE_PROMOTE && (bn == 256 || (bn == 128 && !q2d && !general)) && ew == 8 && no_split &&
+                            q.sk == 128 && pl.out_mode != OUT_QUANT_X;
   if (want_pair == 2 && !pair_epi && !pair_mx && !pair_promote) return MXB_ERR_UNSUPPORTED;
+  if (want_pair == 2 && grp && grp->block_rows % 256) return MXB_ERR_UNSUPPORTED;
   pl.pair = (want_pair == 2) ? 1 : 0;
   if (want_pair == 0 && (pair_epi || pair_mx || pair_promote) && !(cfg && cfg->bn > 0)) {
-    // automatic: pairs pay once there are at least two waves of pair tiles
-    const int pbn = pair_mx ? 224 : 256;
+    // automatic: pairs pay once every pair of SMs has a tile (the one-CTA kernels then need as many rounds of
+    // their half-size tiles, and each of those reads Y from L2 twice). Measured on B200, N = 28672, K = 8192,
+    // per-channel scales: M = 256 (112 pair tiles) 63.5 us against 71.7 us, M = 512 112.6 against 114.7 us.
+    const int pbn = pair_mx ? 224 : bn;
     const long long pair_tiles = static_cast<long long>((pl.rx + 255) / 256) * ((pl.ry + pbn - 1) / pbn);
-    if (pl.rx >= 256 && pair_tiles >= sms) pl.pair = 1;
+    const long long enough = pl.scale_mode == SCALE_EPILOGUE ? sms / 2 : sms;
+    if (pl.rx >= 256 && pair_tiles >= enough && !(grp && grp->block_rows % 256)) pl.pair = 1;
   }
   if (pl.pair && pair_mx) {
     bn = 224;
     pl.bn = bn;
   }
-  pl.kernel = pl.pair ? find_pair_kernel(bn, pl.scale_mode, pl.out_mode, ew)
-                      : find_kernel(bn, pl.scale_mode, pl.out_mode, ew);
+  // Skinny problems on 128-wide tiles whose tile count exceeds the SMs (224 tiles of a 28672-row weight at
+  // M = 128: two rounds with one CTA per SM) run as light CTAs, two per SM.
+  int two_per_sm = 0;
+  if (!pl.pair && !general && pl.scale_mode == SCALE_EPILOGUE && bn == 128 && ew == 4 && pl.out_mode != OUT_QUANT_2D &&
+      pl.ry <= 128 && !(cfg && cfg->splits > 1)) {
+    const long long t128 = static_cast<long long>((pl.rx + 127) / 128) * ((pl.ry + 127) / 128);
+    const int env = light128_override();
+    if (env == 1 || (env < 0 && t128 > sms)) two_per_sm = 1;
+  }
+  pl.kernel = pl.pair ? find_pair_kernel(bn, pl.scale_mode, pl.out_mode, ew, general)
+                      : find_kernel(bn, pl.scale_mode, pl.out_mode, ew, two_per_sm, general);
   if (pl.kernel == nullptr) return MXB_ERR_UNSUPPORTED;
   if (pl.out_mode == OUT_QUANT_Y || q2d) {
     const int cols = bn / (ew / 4);
@@ -345,7 +420,7 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
     pl.fallback_bn = bn > 128 ? 128 : bn;
     int few = pl.fallback_bn >= 128 ? 8 : 4;
     if ((pl.out_mode == OUT_QUANT_Y || q2d) && pl.qy > pl.fallback_bn / (few / 4)) few = 4;
-    pl.fallback = find_kernel(pl.fallback_bn, SCALE_PROMOTE, pl.out_mode, few);
+    pl.fallback = find_kernel(pl.fallback_bn, SCALE_PROMOTE, pl.out_mode, few, 0, general);
     if (pl.fallback == nullptr) return MXB_ERR_UNSUPPORTED;
   }
 
@@ -369,7 +444,7 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
     // Split-K pays only when the tiles alone cannot occupy the GPU (measured on B200: with 224 tiles on
     // 148 SMs every split factor > 1 was slower than none; the exchange costs a few microseconds per
     // unit). Then use as many slices as it takes to give every SM a unit, at least 8 K blocks each.
-    if (split_ok && !pl.pair && 2 * tiles <= pl.ctas && pl.kblocks >= 16) {
+    if (split_ok && !pl.pair && !grp && 2 * tiles <= pl.ctas && pl.kblocks >= 16) {
       int s = pl.ctas / tiles;
       if (s > pl.kblocks / 8) s = pl.kblocks / 8;
       if (s > 16) s = 16;
@@ -385,7 +460,7 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
   // seventh). Their partial sums meet in the workspace like split-K partials.
   pl.tail_first = tiles;
   pl.tail_splits = 1;
-  if (pl.pair && pl.splits == 1 && !(cfg && cfg->splits == 1) && pl.scale_mode != SCALE_MX && split_ok &&
+  if (pl.pair && pl.splits == 1 && !(cfg && cfg->splits == 1) && pl.scale_mode != SCALE_MX && split_ok && !grp &&
       pl.kblocks >= 16) {
     const int clusters = pl.ctas / 2;
     const int rem = clusters > 0 ? tiles % clusters : 0;
@@ -425,7 +500,7 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
     pl.ws_sfx_off = off;
     off += align_up(static_cast<size_t>(pl.sfx_tiles) * pl.kblocks * 512, 256);
     pl.ws_sfy_off = off;
-    off += align_up(static_cast<size_t>(pl.tiles_y) * pl.kblocks * 512 * pl.y_atoms, 256);
+    off += align_up(static_cast<size_t>(pl.tiles_y) * (grp ? grp->groups : 1) * pl.kblocks * 512 * pl.y_atoms, 256);
   }
   if (pl.splits > 1) {
     pl.ws_part_off = off;
@@ -550,9 +625,9 @@ __global__ void selftest_wait_kernel(unsigned int* status) {
 // ---------------------------------------------------------------------------------------------
 static int run_gemm(const mxb_problem_t& q, const mxb_config_t* cfg, const void* left, const void* right,
                     void* out, const void* left_scale, const void* right_scale, void* out_scale,
-                    void* workspace, size_t ws_bytes, cudaStream_t stream) {
+                    void* workspace, size_t ws_bytes, cudaStream_t stream, const GroupArgs* grp = nullptr) {
   Plan pl;
-  int st = choose_plan(q, cfg, pl);
+  int st = choose_plan(q, cfg, pl, grp);
   if (st != MXB_OK) return st;
   const bool quant = (q.flags & MXB_OUT_QUANT) != 0;
   if (!left || !right || !out || !left_scale || !right_scale || (quant && !out_scale)) return MXB_ERR_INVALID;
@@ -567,10 +642,21 @@ static int run_gemm(const mxb_problem_t& q, const mxb_config_t* cfg, const void*
   const void* yp = pl.swap ? left : right;
   const long long xpitch = pl.swap ? q.ldb : q.lda;
   const long long ypitch = pl.swap ? q.lda : q.ldb;
-  st = operand_map(xp, pl.rx, q.k, xpitch, 128, &la.tm_x);
+  st = operand_map(xp, pl.rx, q.k, xpitch, 128, &la.tm_x, pl.x_mn != 0);
   if (st != MXB_OK) return st;
-  st = operand_map(yp, pl.ry, q.k, ypitch, pl.pair ? pl.bn / 2 : pl.bn, &la.tm_y);
+  // grouped: Y is the stack of the groups' [N, K] matrices (densely stacked: group stride N * ldb)
+  const long long y_rows_all = static_cast<long long>(pl.ry) * (grp ? grp->groups : 1);
+  if (grp != nullptr && pl.y_mn) return MXB_ERR_UNSUPPORTED;
+  st = operand_map(yp, y_rows_all, q.k, ypitch, pl.pair ? pl.bn / 2 : pl.bn, &la.tm_y, pl.y_mn != 0);
   if (st != MXB_OK) return st;
+  if (grp != nullptr) {
+    if (grp->group_of_block == nullptr) return MXB_ERR_INVALID;
+    p.x_group = grp->group_of_block;
+    p.group_shift = grp->block_rows == 256 ? 8 : 7;
+    p.group_tiles_y = q.n / pl.bn;
+    // right_scale [groups][N / sn][K / sk]: the next group's scales start (N / sn) rows of scales further
+    p.sy_group_stride = static_cast<long long>(q.n / q.sn) * q.bs_rs;
+  }
 
   p.rx = pl.rx;
   p.ry = pl.ry;
@@ -612,6 +698,8 @@ static int run_gemm(const mxb_problem_t& q, const mxb_config_t* cfg, const void*
   p.pow2_out = (q.flags & MXB_OUT_SCALE_POW2) ? 1 : 0;
   p.fmt_x = q.in_dtype == MXB_E5M2 ? 1 : 0;
   p.fmt_y = p.fmt_x;
+  p.x_mn = pl.x_mn;
+  p.y_mn = pl.y_mn;
   st = status_ptr(&p.status);
   if (st != MXB_OK) return st;
   p.splits = pl.tail_splits > 1 ? pl.tail_splits : pl.splits;
@@ -642,8 +730,9 @@ static int run_gemm(const mxb_problem_t& q, const mxb_config_t* cfg, const void*
     const int report = pl.probe ? 0 : 1;
     {
       PackSide px{p.sx, p.sx_rs, p.sx_ks, pl.rx, 128, 1, pl.sfx_tiles, ws + pl.ws_sfx_off};
-      PackSide py{p.sy, p.sy_rs, p.sy_ks, pl.ry, pl.bn, pl.y_atoms, pl.tiles_y, ws + pl.ws_sfy_off};
-      const long long units = (static_cast<long long>(pl.sfx_tiles) + static_cast<long long>(pl.tiles_y) * pl.y_atoms) *
+      const int y_groups = grp ? grp->groups : 1;
+      PackSide py{p.sy, p.sy_rs, p.sy_ks, pl.ry * y_groups, pl.bn, pl.y_atoms, pl.tiles_y * y_groups, ws + pl.ws_sfy_off};
+      const long long units = (static_cast<long long>(pl.sfx_tiles) + static_cast<long long>(pl.tiles_y) * y_groups * pl.y_atoms) *
                               ((pl.kblocks + PACK_KB - 1) / PACK_KB);
       const int blocks = static_cast<int>(units < 8192 ? units : 8192);
       pack_scale_factors<<<blocks, 256, 0, stream>>>(px, py, p.scale_dtype, kgroups, pl.kblocks, flag, p.status,
@@ -677,9 +766,10 @@ static int run_gemm(const mxb_problem_t& q, const mxb_config_t* cfg, const void*
     fb.p.tiles_x = (pl.rx + 127) / 128;
     fb.p.tiles_y = (pl.ry + pl.fallback_bn - 1) / pl.fallback_bn;
     fb.p.tail_first = fb.p.tiles_x * fb.p.tiles_y;
+    fb.p.group_tiles_y = q.n / pl.fallback_bn;
     fb.p.raster = cfg && cfg->raster > 0 ? cfg->raster : 8;
     if (fb.p.raster > fb.p.tiles_x) fb.p.raster = fb.p.tiles_x;
-    st = operand_map(yp, pl.ry, q.k, ypitch, pl.fallback_bn, &fb.tm_y);
+    st = operand_map(yp, pl.ry, q.k, ypitch, pl.fallback_bn, &fb.tm_y, pl.y_mn != 0);
     if (st != MXB_OK) return st;
     const long long fb_units = static_cast<long long>(fb.p.tiles_x) * fb.p.tiles_y;
     const long long fb_slots = static_cast<long long>(pl.ctas) * pl.fallback->ctas_per_sm;
@@ -780,3 +870,24 @@ extern "C" int mxb_selftest_wait_timeout(void* stream) {
 }
 
 extern "C" unsigned long long mxb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+extern "C" int mxb_grouped_gemm(const mxb_problem_t* problem, const mxb_config_t* cfg, int groups,
+                                const int* group_of_block, int block_rows, const void* left, const void* right,
+                                void* out, const void* left_scale, const void* right_scale, void* out_scale,
+                                void* workspace, size_t workspace_bytes, void* stream) {
+  if (problem == nullptr) return MXB_ERR_INVALID;
+  GroupArgs g{group_of_block, groups, block_rows};
+  return run_gemm(*problem, cfg, left, right, out, left_scale, right_scale, out_scale, workspace, workspace_bytes,
+                  static_cast<cudaStream_t>(stream), &g);
+}
+
+extern "C" int mxb_grouped_query_workspace(const mxb_problem_t* problem, const mxb_config_t* cfg, int groups,
+                                           int block_rows, size_t* bytes) {
+  if (problem == nullptr || bytes == nullptr) return MXB_ERR_INVALID;
+  GroupArgs g{nullptr, groups, block_rows};
+  Plan pl;
+  int st = choose_plan(*problem, cfg, pl, &g);
+  if (st != MXB_OK) return st;
+  *bytes = pl.ws_bytes;
+  return MXB_OK;
+}

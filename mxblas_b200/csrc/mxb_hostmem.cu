@@ -66,6 +66,7 @@ extern "C" int mxb_gemm_host(const mxb_problem_t* problem, const void* left, con
   const bool cs_t = (q.flags & MXB_OUT_SCALE_TRANSPOSE) != 0;
   const int groups = quant ? q.n / q.qn : 0;
   const int qm = quant && q.qm > 1 ? q.qm : 1;  // rows of the result that share a row of output scales
+  if (q.flags & (MXB_LEFT_COL_MAJOR | MXB_RIGHT_ROW_MAJOR)) return MXB_ERR_UNSUPPORTED;  // K-major operands only
   if (q.lda != q.k || q.ldb != q.k) return MXB_ERR_UNSUPPORTED;
   if (q.ldc != (out_t ? q.m : q.n)) return MXB_ERR_UNSUPPORTED;
   if (quant && q.ldcs != (cs_t ? q.m / qm : groups)) return MXB_ERR_UNSUPPORTED;

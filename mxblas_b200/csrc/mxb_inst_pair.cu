@@ -8,7 +8,7 @@ namespace mxb {
 #define MXB_PAIR_ENTRY(BN, SM, OM, EW)                                                                    \
   {                                                                                                       \
     BN, SM, OM, EW, &launch_pair_kernel<PairCfg<BN, SM, OM, EW>>, PairCfg<BN, SM, OM, EW>::SMEM_BYTES,    \
-        PairCfg<BN, SM, OM, EW>::STAGES, 1                                                                \
+        PairCfg<BN, SM, OM, EW>::STAGES, 1, 0, 0                                                          \
   }
 static const KernelEntry kPair[] = {
     MXB_PAIR_ENTRY(256, SCALE_EPILOGUE, OUT_HP, 4),      MXB_PAIR_ENTRY(256, SCALE_EPILOGUE, OUT_HP, 8),
@@ -17,6 +17,7 @@ static const KernelEntry kPair[] = {
     MXB_PAIR_ENTRY(224, SCALE_MX, OUT_HP, 4),            MXB_PAIR_ENTRY(224, SCALE_MX, OUT_QUANT_Y, 4),
     MXB_PAIR_ENTRY(224, SCALE_MX, OUT_QUANT_X, 4),
     MXB_PAIR_ENTRY(256, SCALE_PROMOTE, OUT_HP, 8),       MXB_PAIR_ENTRY(256, SCALE_PROMOTE, OUT_QUANT_Y, 8),
+    MXB_PAIR_ENTRY(128, SCALE_PROMOTE, OUT_HP, 8),       MXB_PAIR_ENTRY(128, SCALE_PROMOTE, OUT_QUANT_Y, 8),
     MXB_PAIR_ENTRY(224, SCALE_EPILOGUE, OUT_HP, 4),      MXB_PAIR_ENTRY(224, SCALE_EPILOGUE, OUT_QUANT_Y, 4),
     MXB_PAIR_ENTRY(224, SCALE_EPILOGUE, OUT_QUANT_X, 4),
 };

@@ -18,7 +18,7 @@ const KernelEntry* quant2d_kernels(int* count) {
 #define MXB_PAIR_ENTRY(BN, SM, OM, EW)                                                                    \
   {                                                                                                       \
     BN, SM, OM, EW, &launch_pair_kernel<PairCfg<BN, SM, OM, EW>>, PairCfg<BN, SM, OM, EW>::SMEM_BYTES,    \
-        PairCfg<BN, SM, OM, EW>::STAGES, 1                                                                \
+        PairCfg<BN, SM, OM, EW>::STAGES, 1, 0, 0                                                          \
   }
 static const KernelEntry kQuant2dPair[] = {
     MXB_PAIR_ENTRY(256, SCALE_EPILOGUE, OUT_QUANT_2D, 8),

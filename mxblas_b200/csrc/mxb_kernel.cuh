@@ -54,6 +54,17 @@ struct GemmParams {
   int qx, qy;                // OUT_QUANT_2D: a quantisation block is qx rows of X by qy columns of Y
   int pow2_out;              // round output scales up to a power of two
   int fmt_x, fmt_y;          // 0 = e4m3, 1 = e5m2
+  // Operand storage: 0 = K-major ([rows, K], unit stride along K: the reference's only form), 1 = row-major
+  // along the rows ([K, rows], unit stride along the operand's rows: a column-major `left`, a row-major `right`).
+  // The tensor map of such an operand has the rows as its inner dimension and a 128 x 128 box.
+  int x_mn, y_mn;
+  // Grouped GEMM (one weight matrix per group, rows of X sorted by group): x_group[b] is the group of block b of
+  // 2^group_shift rows of X, or -1 for a block to skip; Y is the stack [groups * ry, K] of the groups' matrices,
+  // a tile of group g reads Y tile  ty + g * group_tiles_y  (ry is a multiple of the tile width) and the scales
+  // of Y that start  g * sy_group_stride  elements further. nullptr: plain GEMM.
+  const int* x_group;
+  int group_shift, group_tiles_y;
+  long long sy_group_stride;
   unsigned int* status;      // device status word (0 = ok)
   const unsigned int* gate;  // optional: run only if *gate == gate_value (device-side dispatch)
   unsigned int gate_value;
@@ -94,8 +105,14 @@ __device__ __forceinline__ float group_scale(float amax, float inv_fp8_max, int 
   return s;
 }
 
-template <int BN_, int SCALE_MODE_, int OUT_MODE_, int EPI_WARPS_>
+// TWO_PER_SM_: a 128-wide tile with scales applied in the epilogue as a "light" CTA, two per SM with three
+// shared-memory stages each (narrower tiles are light by themselves, see LIGHT below).
+// GENERAL_: the instantiation also handles operands stored along their rows (column-major left, row-major
+// right) and grouped GEMMs. The plain instantiations compile those paths out: as run-time branches they cost
+// the kernels of the reference's own layout 4 % (same-box A/B on B200: 8192^3 per-tensor 364.5 -> 380 us).
+template <int BN_, int SCALE_MODE_, int OUT_MODE_, int EPI_WARPS_, bool TWO_PER_SM_ = false, bool GENERAL_ = false>
 struct KernelCfg {
+  static constexpr bool GENERAL = GENERAL_;
   static constexpr int BM = 128, BK = 128;
   static constexpr int BN = BN_;
   static constexpr int SCALE_MODE = SCALE_MODE_;
@@ -127,15 +144,19 @@ struct KernelCfg {
   // with four stages each: twice as many tiles stream concurrently, which takes the edge off wave
   // quantisation (224 tiles of config 5 no longer need two rounds on 148 SMs). Such a CTA takes
   // only the 128 TMEM columns it needs, so that two fit.
-  static constexpr bool LIGHT = BN <= 64 && SCALE_MODE == SCALE_EPILOGUE;
+  static constexpr bool LIGHT = (BN <= 64 || (BN == 128 && TWO_PER_SM_)) && SCALE_MODE == SCALE_EPILOGUE;
+  static_assert(!TWO_PER_SM_ || LIGHT, "two CTAs per SM: 128-wide tiles with scales applied in the epilogue");
   static constexpr int CTAS_PER_SM = LIGHT ? 2 : 1;
-  static constexpr int STAGES = LIGHT ? 4 : ((STAGES_FIT > 8 ? 8 : STAGES_FIT) & ~1);
+  static constexpr int STAGES = LIGHT ? (BN == 128 ? 3 : 4) : ((STAGES_FIT > 8 ? 8 : STAGES_FIT) & ~1);
+  // one full barrier per PAIR of stages (the MMA thread's wait costs it ~200 cycles), where the stage count is
+  // even; the three-stage light CTA, bound by HBM and not by MMA issue, has one per stage
+  static constexpr bool PAIRED_FULL = (STAGES % 2) == 0;
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + AUX_BYTES;
   // TMEM plan (512 columns allocated): accumulator buffers every ACC_STRIDE columns; the MX scale
   // factors live in columns the accumulators leave free.
-  static constexpr int ACC_STRIDE = LIGHT ? 64 : (BN <= 128 ? 128 : 256);
+  static constexpr int ACC_STRIDE = LIGHT ? (BN == 128 ? 128 : 64) : (BN <= 128 ? 128 : 256);
   static constexpr int NUM_ACC = LIGHT ? 2 : (SCALE_MODE == SCALE_MX ? 2 : 512 / ACC_STRIDE);
-  static constexpr int TMEM_COLS = LIGHT ? 128 : 512;
+  static constexpr int TMEM_COLS = LIGHT ? 2 * ACC_STRIDE : 512;
   static constexpr int SFA_COL = BN <= 128 ? 256 : 224;  // MX only (BN <= 128 or BN == 224)
   static constexpr int SFB_COL = SFA_COL + 4;
   static constexpr int SF_SLOT = 16;                     // column distance of the two scale-factor slots
@@ -168,6 +189,17 @@ __device__ __forceinline__ TileCoord tile_coord(int t, const GemmParams& p) {
   c.ty = r / gsz;
   return c;
 }
+
+// Group of the X rows of a tile whose first row is `row0` (grouped GEMM); 0 for a plain GEMM, negative: skip.
+template <class Cfg>
+__device__ __forceinline__ int tile_group(const GemmParams& p, int row0) {
+  if constexpr (!Cfg::GENERAL) return 0;
+  return p.x_group != nullptr ? __ldg(p.x_group + (row0 >> p.group_shift)) : 0;
+}
+template <class Cfg>
+__device__ __forceinline__ bool x_by_rows(const GemmParams& p) { return Cfg::GENERAL && p.x_mn != 0; }
+template <class Cfg>
+__device__ __forceinline__ bool y_by_rows(const GemmParams& p) { return Cfg::GENERAL && p.y_mn != 0; }
 
 // ---------------------------------------------------------------------------------------------
 // Output stage: converts one thread's row slice (CHUNKS * 32 consecutive y columns of x row `xrow`)
@@ -572,8 +604,8 @@ struct OutputStage {
 template <class Cfg, class WaitFn, class PeekFn, class ReleaseFn>
 __device__ __forceinline__ bool promote_groups(const GemmParams& p, float (&acc)[Cfg::COLS_PER_THREAD], int xrow,
                                                int ycol0, int kbeg, int kend, int e, int lane, uint32_t ta_base,
-                                               uint32_t& acc_it, float* sYs, WaitFn wait_group, PeekFn peek_group,
-                                               ReleaseFn release_group) {
+                                               uint32_t& acc_it, float* sYs, long long sy_goff, WaitFn wait_group,
+                                               PeekFn peek_group, ReleaseFn release_group) {
   bool ok = true;
   const int ngroups = (kend - kbeg + p.gk - 1) / p.gk;
   const int g0 = kbeg / p.gk;
@@ -610,7 +642,7 @@ __device__ __forceinline__ bool promote_groups(const GemmParams& p, float (&acc)
 #pragma unroll
     for (int c = 0; c < Cfg::CHUNKS; ++c) {
       const int y = ycol0 + c * 32;
-      dst[c] = (y < p.ry && gi < nvalid) ? load_scale(p.sy, (y / p.gy) * p.sy_rs + g * p.sy_ks, dt) : 0.f;
+      dst[c] = (y < p.ry && gi < nvalid) ? load_scale(p.sy, sy_goff + (y / p.gy) * p.sy_rs + g * p.sy_ks, dt) : 0.f;
     }
   };
   float sx_c = fetch_sx(0), sx_n1 = fetch_sx(1);
@@ -635,10 +667,11 @@ __device__ __forceinline__ bool promote_groups(const GemmParams& p, float (&acc)
     }
   };
 
-  bool next_ready = false;  // lane 0: the next group's barrier was already seen complete
-#pragma unroll 1
-  for (int gi = 0; gi < ngroups; ++gi) {
-    const float sx_n2 = fetch_sx(gi + 2);  // in flight for two groups
+  // Per-group scale upkeep, shared by both loop forms below: before group gi's arithmetic the X scale of group
+  // gi + 2 is requested and the Y scales are refreshed; after it the X-scale registers rotate.
+  float sx_n2 = 0.f;
+  auto scales_begin = [&](int gi) {
+    sx_n2 = fetch_sx(gi + 2);  // in flight for two groups
     if (y_uniform) {
       if ((gi & 31) == 0 && gi + 32 < ngroups) load_sy_lane(gi / 32 + 1, sy_lane_nxt);
     } else if ((gi % PB) == 0) {
@@ -647,10 +680,24 @@ __device__ __forceinline__ bool promote_groups(const GemmParams& p, float (&acc)
         const int j = idx / Cfg::COLS_PER_THREAD, col = idx - j * Cfg::COLS_PER_THREAD;
         const int gj = gi + j, g = g0 + gj, y = ycol0 + col;
         sy_stage[idx] =
-            (y < p.ry && gj < nvalid) ? load_scale(p.sy, (y / p.gy) * p.sy_rs + g * p.sy_ks, dt) : 0.f;
+            (y < p.ry && gj < nvalid) ? load_scale(p.sy, sy_goff + (y / p.gy) * p.sy_rs + g * p.sy_ks, dt) : 0.f;
       }
       __syncwarp();
     }
+  };
+  auto scales_end = [&](int gi) {
+    if (y_uniform && (gi & 31) == 31) {
+#pragma unroll
+      for (int c = 0; c < Cfg::CHUNKS; ++c) sy_lane[c] = sy_lane_nxt[c];
+    }
+    sx_c = sx_n1;
+    sx_n1 = sx_n2;
+  };
+
+  bool next_ready = false;  // lane 0: the next group's barrier was already seen complete
+#pragma unroll 1
+  for (int gi = 0; gi < ngroups; ++gi) {
+    scales_begin(gi);
     const uint32_t b = acc_it % Cfg::NUM_ACC;
     uint32_t okw = 1u;
     if (lane == 0) okw = (next_ready || wait_group(acc_it)) ? 1u : 0u;
@@ -701,12 +748,7 @@ __device__ __forceinline__ bool promote_groups(const GemmParams& p, float (&acc)
       promote_chunk(r1, 3, gi, sx_c);
     }
     ++acc_it;
-    if (y_uniform && (gi & 31) == 31) {
-#pragma unroll
-      for (int c = 0; c < Cfg::CHUNKS; ++c) sy_lane[c] = sy_lane_nxt[c];
-    }
-    sx_c = sx_n1;
-    sx_n1 = sx_n2;
+    scales_end(gi);
   }
   return ok;
 }
@@ -794,7 +836,8 @@ mx_gemm_sm100(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(bar_full + 8 * s, 2);  // covers stages s and s+1 (even s only): one arrival per stage
+      // paired: covers stages s and s+1 (even s only), one arrival per stage
+      mbar_init(bar_full + 8 * s, Cfg::PAIRED_FULL ? 2 : 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int b = 0; b < NUM_ACC; ++b) {
@@ -835,19 +878,30 @@ mx_gemm_sm100(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
         const int t = u / splits, sp = u - t * splits;
         const TileCoord tc = tile_coord(t, p);
+        const int grp = tile_group<Cfg>(p, tc.tx * 128);
+        if (grp < 0) continue;  // every role skips the same tiles
+        const int ty_in = tc.ty + grp * p.group_tiles_y;
         const int kb0 = kb_lo(sp), kb1 = kb_lo(sp + 1);
         for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, DEV_TIMEOUT_PRODUCER);
           if (!ok) break;
-          const uint32_t fb = bar_full + 8 * (s & ~1u);
+          const uint32_t fb = bar_full + 8 * (Cfg::PAIRED_FULL ? (s & ~1u) : s);
           mbar_expect_tx(fb, Cfg::STAGE_BYTES);
-          tma_load_2d(smem_u32(sA + s * Cfg::A_BYTES), &tm_x, fb, kb * 128, tc.tx * 128);
-          tma_load_2d(smem_u32(sB + s * Cfg::B_BYTES), &tm_y, fb, kb * 128, tc.ty * BN);
+          if (x_by_rows<Cfg>(p)) tma_load_2d(smem_u32(sA + s * Cfg::A_BYTES), &tm_x, fb, tc.tx * 128, kb * 128);
+          else tma_load_2d(smem_u32(sA + s * Cfg::A_BYTES), &tm_x, fb, kb * 128, tc.tx * 128);
+          if (y_by_rows<Cfg>(p)) {
+            // one 128 x 128 box per 128 rows of Y (the host only plans tile widths of 128 and 256 here)
+#pragma unroll
+            for (int j = 0; j < Cfg::Y_ATOMS; ++j)
+              tma_load_2d(smem_u32(sB + s * Cfg::B_BYTES + j * 16384), &tm_y, fb, ty_in * BN + j * 128, kb * 128);
+          } else {
+            tma_load_2d(smem_u32(sB + s * Cfg::B_BYTES), &tm_y, fb, kb * 128, ty_in * BN);
+          }
           if constexpr (Cfg::SCALE_MODE == SCALE_MX) {
             bulk_load_1d(smem_u32(sSFA + s * Cfg::SFA_BYTES),
                          p.sfx + (static_cast<size_t>(tc.tx) * p.kblocks + kb) * 512, 512, fb);
             bulk_load_1d(smem_u32(sSFB + s * Cfg::SFB_BYTES),
-                         p.sfy + (static_cast<size_t>(tc.ty) * p.kblocks + kb) * Cfg::SFB_BYTES,
+                         p.sfy + (static_cast<size_t>(ty_in) * p.kblocks + kb) * Cfg::SFB_BYTES,
                          Cfg::SFB_BYTES, fb);
           }
           if (++s == STAGES) {
@@ -857,7 +911,7 @@ mx_gemm_sm100(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         }
       }
       // an odd total leaves the last stage pair half filled: complete it with a plain arrival
-      if (ok && (s & 1)) mbar_arrive(bar_full + 8 * (s & ~1u));
+      if (Cfg::PAIRED_FULL && ok && (s & 1)) mbar_arrive(bar_full + 8 * (s & ~1u));
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -869,18 +923,25 @@ mx_gemm_sm100(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       uint32_t s = 0, ph = 0;        // smem stage / phase
       uint32_t b = 0, aph = 0;       // accumulator buffer / phase
       bool ok = true;
-      const uint32_t idesc = Cfg::SCALE_MODE == SCALE_MX ? umma_idesc_mxf8(128, BN, p.fmt_x, p.fmt_y)
-                                                         : umma_idesc_f8(128, BN, p.fmt_x, p.fmt_y);
+      const uint32_t idesc = umma_idesc_major(Cfg::SCALE_MODE == SCALE_MX ? umma_idesc_mxf8(128, BN, p.fmt_x, p.fmt_y)
+                                                                          : umma_idesc_f8(128, BN, p.fmt_x, p.fmt_y),
+                                              x_by_rows<Cfg>(p), y_by_rows<Cfg>(p));
+      // descriptor step from one 32-deep K slice to the next: 32 bytes along a K-major row, four 8-row groups
+      // (4096 bytes) in an operand staged as K rows
+      const uint32_t kstep_a = x_by_rows<Cfg>(p) ? 256u : 2u, kstep_b = y_by_rows<Cfg>(p) ? 256u : 2u;
+      const uint64_t ka[4] = {0, kstep_a, 2 * kstep_a, 3 * kstep_a}, kbs[4] = {0, kstep_b, 2 * kstep_b, 3 * kstep_b};
+      const uint64_t hi_a = umma_desc_hi(x_by_rows<Cfg>(p)), hi_b = umma_desc_hi(y_by_rows<Cfg>(p));
       // K elements accumulated in TMEM before the epilogue warps take the partial sum
       const int group_k = Cfg::SCALE_MODE == SCALE_PROMOTE ? p.gk : 0;
       for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
         const int t = u / splits, sp = u - t * splits;
+        if (Cfg::GENERAL && p.x_group != nullptr && tile_group<Cfg>(p, tile_coord(t, p).tx * 128) < 0) continue;
         const int kb0 = kb_lo(sp), kb1 = kb_lo(sp + 1);
         uint32_t d_tmem = 0;
         int gpos = 0;       // K elements already in the open scale group (split ranges start on a group)
         bool open = false;  // an accumulator buffer is currently being filled
         for (int kb = kb0; kb < kb1 && ok; ++kb) {
-          if ((s & 1) == 0) {  // both stages of the pair have landed once this barrier completes
+          if (!Cfg::PAIRED_FULL || (s & 1) == 0) {  // paired: both stages have landed once this barrier completes
             ok = mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL);
             if (!ok) break;
             tc_fence_after();
@@ -905,7 +966,7 @@ mx_gemm_sm100(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
           }
           const uint32_t a_addr = smem_u32(sA + s * Cfg::A_BYTES);
           const uint32_t b_addr = smem_u32(sB + s * Cfg::B_BYTES);
-          const uint64_t da0 = umma_desc_k128(a_addr), db0 = umma_desc_k128(b_addr);
+          const uint64_t da0 = umma_desc_at(hi_a, a_addr), db0 = umma_desc_at(hi_b, b_addr);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             bool fresh = false;
@@ -917,8 +978,7 @@ mx_gemm_sm100(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
               open = true;
               fresh = true;
             }
-            // the next 32-element K slice sits 32 bytes further: +2 in the descriptors' address field
-            const uint64_t da = da0 + 2 * kk, db = db0 + 2 * kk;
+            const uint64_t da = da0 + ka[kk], db = db0 + kbs[kk];
             if constexpr (Cfg::SCALE_MODE == SCALE_MX) {
               umma_mxf8(d_tmem, da, db, umma_idesc_sf_ids(idesc, kk, kk), fresh ? 0u : 1u,
                         tmem_base + Cfg::SFA_COL + (s & 1) * Cfg::SF_SLOT,
@@ -967,6 +1027,9 @@ mx_gemm_sm100(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
     for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
       const int t = u / splits, sp = u - t * splits;
       const TileCoord tc = tile_coord(t, p);
+      const int grp = tile_group<Cfg>(p, tc.tx * 128);
+      if (grp < 0) continue;
+      const long long sy_goff = Cfg::GENERAL ? grp * p.sy_group_stride : 0;
       const int xrow = tc.tx * 128 + quad * 32 + lane;
       const int ycol0 = tc.ty * BN + slice * Cfg::COLS_PER_THREAD;
       const int kb0 = kb_lo(sp), kb1 = kb_lo(sp + 1);
@@ -981,7 +1044,7 @@ mx_gemm_sm100(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         // K range padded to whole blocks: the MMA warp closes a buffer per group
         ok = promote_groups<Cfg>(
             p, acc, xrow, ycol0, kb0 * 128, kb1 * 128, e, lane,
-            tmem_base + lane_addr + slice * Cfg::COLS_PER_THREAD, acc_it, sYs,
+            tmem_base + lane_addr + slice * Cfg::COLS_PER_THREAD, acc_it, sYs, sy_goff,
             [&](uint32_t it) {
               return mbar_wait(bar_tfull + 8 * (it % NUM_ACC), (it / NUM_ACC) & 1, abort_flag, p.status,
                                DEV_TIMEOUT_EPILOGUE);
@@ -1014,7 +1077,7 @@ mx_gemm_sm100(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
           __syncwarp();  // the previous tile's readers of my_sy are done
           for (int j = lane; j < Cfg::COLS_PER_THREAD; j += 32) {
             const int y = ycol0 + j;
-            my_sy[j] = y < p.ry ? load_scale(p.sy, (y / p.gy) * p.sy_rs, p.scale_dtype) : 0.f;
+            my_sy[j] = y < p.ry ? load_scale(p.sy, sy_goff + (y / p.gy) * p.sy_rs, p.scale_dtype) : 0.f;
           }
           __syncwarp();
           sy_ptr = my_sy;

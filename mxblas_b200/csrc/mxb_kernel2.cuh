@@ -39,8 +39,9 @@ namespace mxb {
 // next to the two accumulator buffers; with scales constant along K the narrower tile exists as a
 // configuration: the MMAs are bound by shared-memory traffic, which shrinks by 6 % only, so saving a wave of
 // tiles with it measured no faster). Each CTA stages BN/2 rows of Y.
-template <int BN_, int SCALE_MODE_, int OUT_MODE_, int EPI_WARPS_>
+template <int BN_, int SCALE_MODE_, int OUT_MODE_, int EPI_WARPS_, bool GENERAL_ = false>
 struct PairCfg {
+  static constexpr bool GENERAL = GENERAL_;  // operands stored along their rows and grouped GEMMs (see KernelCfg)
   static constexpr int BN = BN_;
   static constexpr int BM_PAIR = 256;      // rows of the pair's tile (each CTA owns 128)
   static constexpr int SCALE_MODE = SCALE_MODE_;
@@ -68,10 +69,13 @@ struct PairCfg {
   static constexpr int XMAX_BYTES = 2 * 2 * 4 * 32 * 4;
   static constexpr int BAR_BYTES = 512;
   static constexpr int AUX_BYTES = YS_BYTES + XMAX_BYTES + BAR_BYTES;
-  static constexpr int STAGES = 6;
+  // 128-column tiles (promotion only): four accumulator buffers of 128 columns, so that a promotion warp may
+  // run three K blocks behind the MMAs, and every thread's 64 columns of a partial sum fit in registers at
+  // once: the buffer goes back to the MMA thread after ONE TMEM round trip instead of three
+  static constexpr int STAGES = BN <= 128 ? 8 : 6;
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + AUX_BYTES;
-  static constexpr int ACC_STRIDE = 256;
-  static constexpr int NUM_ACC = 2;
+  static constexpr int ACC_STRIDE = BN <= 128 ? 128 : 256;
+  static constexpr int NUM_ACC = 512 / ACC_STRIDE;
   // MX: four scale-factor slots of 16 columns (X factors in columns 0..3 of a slot, Y factors in
   // 4..11) in the columns the two 224-wide accumulators leave free: 224..255 and 480..511
   static constexpr int SF_SLOTS = 4, SFB_OFFSET = 4;
@@ -80,7 +84,8 @@ struct PairCfg {
   }
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
   static_assert(STAGES % 2 == 0, "full barriers cover stage pairs");
-  static_assert(BN == 256 || (BN == 224 && SCALE_MODE != SCALE_PROMOTE), "tile widths of the pair kernel");
+  static_assert(BN == 256 || (BN == 224 && SCALE_MODE != SCALE_PROMOTE) || (BN == 128 && SCALE_MODE == SCALE_PROMOTE),
+                "tile widths of the pair kernel");
   static_assert(NUM_ACC * ACC_STRIDE <= 512 && STAGES > NUM_ACC, "promotion: a stage's barrier is observed before it turns again");
   static_assert(SCALE_MODE != SCALE_MX || BN == 224, "block-scaled pairs use 224 columns");
   static_assert(COLS_PER_THREAD % 32 == 0, "whole 32-column chunks per epilogue thread");
@@ -181,15 +186,20 @@ mx_gemm_sm100_pair(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       for (int u = pair; u < num_units && ok; u += num_pairs) {
         const PairUnit un = pair_unit(u, p);
         const TileCoord tc = tile_coord(un.t, p);
+        const int grp = tile_group<Cfg>(p, tc.tx * 256);  // grouped GEMM: blocks of whole 256-row tiles
+        if (grp < 0) continue;
         const int xr = tc.tx * 256 + static_cast<int>(rank) * 128;
-        const int yr = tc.ty * BN + static_cast<int>(rank) * (BN / 2);
+        const int yr = (tc.ty + grp * p.group_tiles_y) * BN + static_cast<int>(rank) * (BN / 2);
         for (int kb = un.kb0; kb < un.kb1; ++kb) {
           ok = mbar_wait_cluster(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, DEV_TIMEOUT_PRODUCER);
           if (!ok) break;
           const uint32_t fb = fb0 + 8 * (s & ~1u);
           mbar_expect_tx_cluster(fb, Cfg::STAGE_BYTES);
-          tma_load_2d_pair(smem_u32(sA + s * Cfg::A_BYTES), &tm_x, fb, kb * 128, xr);
-          tma_load_2d_pair(smem_u32(sB + s * Cfg::B_BYTES), &tm_y, fb, kb * 128, yr);
+          if (x_by_rows<Cfg>(p)) tma_load_2d_pair(smem_u32(sA + s * Cfg::A_BYTES), &tm_x, fb, xr, kb * 128);
+          else tma_load_2d_pair(smem_u32(sA + s * Cfg::A_BYTES), &tm_x, fb, kb * 128, xr);
+          // (an operand stored along its rows is only planned with 256-wide tiles: this CTA's half is one box)
+          if (y_by_rows<Cfg>(p)) tma_load_2d_pair(smem_u32(sB + s * Cfg::B_BYTES), &tm_y, fb, yr, kb * 128);
+          else tma_load_2d_pair(smem_u32(sB + s * Cfg::B_BYTES), &tm_y, fb, kb * 128, yr);
           if (++s == STAGES) {
             s = 0;
             ph ^= 1;
@@ -207,10 +217,15 @@ mx_gemm_sm100_pair(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       uint32_t s = 0, ph = 0, b = 0, aph = 0;
       uint32_t slot = 0;  // block-scaled: TMEM scale-factor slot of the current stage
       bool ok = true;
-      const uint32_t idesc = Cfg::SCALE_MODE == SCALE_MX ? umma_idesc_mxf8(256, BN, p.fmt_x, p.fmt_y)
-                                                         : umma_idesc_f8(256, BN, p.fmt_x, p.fmt_y);
+      const uint32_t idesc = umma_idesc_major(Cfg::SCALE_MODE == SCALE_MX ? umma_idesc_mxf8(256, BN, p.fmt_x, p.fmt_y)
+                                                                          : umma_idesc_f8(256, BN, p.fmt_x, p.fmt_y),
+                                              x_by_rows<Cfg>(p), y_by_rows<Cfg>(p));
+      const uint32_t kstep_a = x_by_rows<Cfg>(p) ? 256u : 2u, kstep_b = y_by_rows<Cfg>(p) ? 256u : 2u;
+      const uint64_t ka[4] = {0, kstep_a, 2 * kstep_a, 3 * kstep_a}, kbs[4] = {0, kstep_b, 2 * kstep_b, 3 * kstep_b};
+      const uint64_t hi_a = umma_desc_hi(x_by_rows<Cfg>(p)), hi_b = umma_desc_hi(y_by_rows<Cfg>(p));
       for (int u = pair; u < num_units && ok; u += num_pairs) {
         const PairUnit un = pair_unit(u, p);
+        if (Cfg::GENERAL && p.x_group != nullptr && tile_group<Cfg>(p, tile_coord(un.t, p).tx * 256) < 0) continue;
         if constexpr (Cfg::SCALE_MODE != SCALE_PROMOTE) {
           ok = mbar_wait_cluster(bar_tempty + 8 * b, aph ^ 1, abort_flag, p.status, DEV_TIMEOUT_MMA_TMEM);
           if (!ok) break;
@@ -230,24 +245,25 @@ mx_gemm_sm100_pair(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             tc_fence_after();
             d_tmem = tmem_base + b * Cfg::ACC_STRIDE;
           }
-          const uint64_t da0 = umma_desc_k128(smem_u32(sA + s * Cfg::A_BYTES));
-          const uint64_t db0 = umma_desc_k128(smem_u32(sB + s * Cfg::B_BYTES));
+          const uint64_t da0 = umma_desc_at(hi_a, smem_u32(sA + s * Cfg::A_BYTES));
+          const uint64_t db0 = umma_desc_at(hi_b, smem_u32(sB + s * Cfg::B_BYTES));
           if constexpr (Cfg::SCALE_MODE == SCALE_MX) {
             // the stage's scale factors are in TMEM slot `slot` of both CTAs (the full barrier counted
             // the scale-factor warps' arrivals)
             const uint32_t sf = tmem_base + Cfg::sf_col(slot);
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
-              umma_mxf8_pair(d_tmem, da0 + 2 * kk, db0 + 2 * kk, umma_idesc_sf_ids(idesc, kk, kk),
+              umma_mxf8_pair(d_tmem, da0 + ka[kk], db0 + kbs[kk], umma_idesc_sf_ids(idesc, kk, kk),
                              (kb > un.kb0 || kk != 0) ? 1u : 0u, sf, sf + Cfg::SFB_OFFSET);
             slot = (slot + 1) & (Cfg::SF_SLOTS - 1);
           } else if constexpr (Cfg::SCALE_MODE == SCALE_PROMOTE) {
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) umma_f8_pair(d_tmem, da0 + 2 * kk, db0 + 2 * kk, idesc, kk != 0 ? 1u : 0u);
+            for (int kk = 0; kk < 4; ++kk)
+              umma_f8_pair(d_tmem, da0 + ka[kk], db0 + kbs[kk], idesc, kk != 0 ? 1u : 0u);
           } else {
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
-              umma_f8_pair(d_tmem, da0 + 2 * kk, db0 + 2 * kk, idesc, (kb > un.kb0 || kk != 0) ? 1u : 0u);
+              umma_f8_pair(d_tmem, da0 + ka[kk], db0 + kbs[kk], idesc, (kb > un.kb0 || kk != 0) ? 1u : 0u);
           }
           // the stage is free in both CTAs once these MMAs have read it (promotion: and the partial
           // sum of this K block is complete)
@@ -380,6 +396,9 @@ mx_gemm_sm100_pair(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     for (int u = pair; u < num_units && ok; u += num_pairs) {
       const PairUnit un = pair_unit(u, p);
       const TileCoord tc = tile_coord(un.t, p);
+      const int grp = tile_group<Cfg>(p, tc.tx * 256);
+      if (grp < 0) continue;
+      const long long sy_goff = Cfg::GENERAL ? grp * p.sy_group_stride : 0;
       const int xrow = tc.tx * 256 + static_cast<int>(rank) * 128 + quad * 32 + lane;
       const int ycol0 = tc.ty * BN + slice * Cfg::COLS_PER_THREAD;
       // K-sliced tiles: this thread's first value in slice unit `slot` of the workspace,
@@ -402,7 +421,7 @@ mx_gemm_sm100_pair(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         const uint32_t tempty0 = map_to_cta(bar_tempty, 0);
         ok = promote_groups<Cfg>(
             p, acc, xrow, ycol0, un.kb0 * 128, un.kb1 * 128, e, lane,
-            tmem_base + lane_addr + slice * Cfg::COLS_PER_THREAD, acc_it, sYs,
+            tmem_base + lane_addr + slice * Cfg::COLS_PER_THREAD, acc_it, sYs, sy_goff,
             // partial sum number `it` of this CTA is complete when the commit of its K block arrives on the
             // stage's empty barrier: stage it % STAGES, turn it / STAGES
             [&](uint32_t it) {
@@ -432,7 +451,7 @@ mx_gemm_sm100_pair(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         __syncwarp();
         for (int j = lane; j < Cfg::COLS_PER_THREAD; j += 32) {
           const int y = ycol0 + j;
-          my_sy[j] = y < p.ry ? load_scale(p.sy, (y / p.gy) * p.sy_rs, p.scale_dtype) : 0.f;
+          my_sy[j] = y < p.ry ? load_scale(p.sy, sy_goff + (y / p.gy) * p.sy_rs, p.scale_dtype) : 0.f;
         }
         __syncwarp();
         sy_ptr = my_sy;

@@ -190,6 +190,35 @@ __device__ __forceinline__ uint64_t umma_desc_k128(uint32_t addr) {
   return d;
 }
 
+// The same for an operand tile that is contiguous along M (or N) instead of K, as a column-major `left` or a
+// row-major `right` is: the tile is staged as K rows of 128 bytes (128 consecutive rows of the operand per K
+// element) with the 128-byte swizzle; groups of eight K rows lie 1024 bytes apart (stride byte offset) and
+// the next 128 operand rows start one whole staged block of `block_bytes` later (leading byte offset). The
+// matching instruction-descriptor bit (umma_idesc_major) tells the MMA which form an operand has.
+__device__ __forceinline__ uint64_t umma_desc_mn128(uint32_t addr, uint32_t block_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr >> 4) & 0x3FFF);
+  d |= static_cast<uint64_t>((block_bytes >> 4) & 0x3FFF) << 16;  // leading byte offset: next 128 rows of the operand
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;                    // stride byte offset: next group of eight K rows
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+// The MMA-issuing thread is a serial resource (every instruction between two MMAs is exposed), so per stage it
+// only ORs the stage's address into a descriptor whose constant bits were chosen once, outside the loops:
+// umma_desc_hi gives those bits for either operand form, umma_desc_at adds the address.
+__device__ __forceinline__ uint64_t umma_desc_hi(int mn_major) {
+  return mn_major ? (umma_desc_mn128(0, 16384)) : (umma_desc_k128(0));
+}
+__device__ __forceinline__ uint64_t umma_desc_at(uint64_t hi, uint32_t addr) {
+  return hi | static_cast<uint64_t>((addr >> 4) & 0x3FFF);
+}
+
+// instruction-descriptor bits for operands that are M-/N-major (bit 15: A, bit 16: B); valid for the 8-bit types
+__host__ __device__ constexpr uint32_t umma_idesc_major(uint32_t idesc, int a_mn, int b_mn) {
+  return idesc | (static_cast<uint32_t>(a_mn ? 1 : 0) << 15) | (static_cast<uint32_t>(b_mn ? 1 : 0) << 16);
+}
+
 // Descriptor for an un-swizzled block of rows of 16 bytes each (8-row groups 128 bytes apart),
 // the source format of the scale-factor copy tcgen05.cp.32x128b.
 __device__ __forceinline__ uint64_t umma_desc_rows16(uint32_t addr) {

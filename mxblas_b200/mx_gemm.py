@@ -62,6 +62,8 @@ class _Meta(NamedTuple):
     as_ks: int
     bs_rs: int
     bs_ks: int
+    left_col_major: bool = False
+    right_row_major: bool = False
 
 
 def _is_row_major(stride, size) -> bool:
@@ -169,18 +171,24 @@ def get_meta_info(
             )
     else:
         qm, qn = 0, 0  # a quant_size passed without output_quant is accepted and ignored
-    # layouts (mx_gemm.py:50-58, mxblas/gemm/template.py:70-85): left row-major, right column-major
+    # Layouts (mx_gemm.py:50-58). The reference's templates match only a row-major left and a column-major right
+    # (mxblas/gemm/template.py:70-73, "No matching template" otherwise); here a column-major left (the .T view of
+    # a [K, M] tensor) and a row-major right (a [K, N] tensor as stored) are accepted as well: the operand
+    # layouts of a backward pass (dX = dY . W, dW = dY^T . X).
     for stride in (left_stride, right_stride, left_scale_stride, right_scale_stride):
         assert stride[0] == 1 or stride[1] == 1, "You should not reach here, stride is not valid."
-    if not _is_row_major(left_stride, left_size):
-        raise ValueError("No matching kernel: left must be row-major ([M, K] with unit stride along K).")
-    if not _is_col_major(right_stride, right_size):
-        raise ValueError(
-            "No matching kernel: right must be the column-major view of a [N, K] tensor (pass b.T)."
-        )
-    lda = left_stride[0] if m > 1 else max(left_stride[0], k)
-    ldb = right_stride[1] if n > 1 else max(right_stride[1], k)
-    if k % 16 != 0 or lda % 16 != 0 or ldb % 16 != 0 or lda < k or ldb < k:
+    left_col_major = not _is_row_major(left_stride, left_size)
+    right_row_major = not _is_col_major(right_stride, right_size)
+    if left_col_major:
+        lda, lda_min = (left_stride[1] if k > 1 else max(left_stride[1], m)), m
+    else:
+        lda, lda_min = (left_stride[0] if m > 1 else max(left_stride[0], k)), k
+    if right_row_major:
+        ldb, ldb_min = (right_stride[0] if k > 1 else max(right_stride[0], n)), n
+    else:
+        ldb, ldb_min = (right_stride[1] if n > 1 else max(right_stride[1], k)), k
+    if lda % 16 != 0 or ldb % 16 != 0 or lda < lda_min or ldb < ldb_min or \
+            (k % 16 != 0 and not (left_col_major and right_row_major)):
         raise ValueError(
             f"No matching kernel: K ({k}) and the row pitches of left ({lda}) and right ({ldb}) "
             "must be multiples of 16 bytes (TMA)."
@@ -191,6 +199,7 @@ def get_meta_info(
         m, n, k, sm, sn, sk, qm, qn, left_dtype, out_dtype, left_scale_dtype, bool(output_quant),
         bool(out_transpose), bool(out_scale_transpose), lda, ldb,
         left_scale_stride[0], left_scale_stride[1], right_scale_stride[1], right_scale_stride[0],
+        left_col_major, right_row_major,
     )  # fmt: skip
 
 
@@ -208,6 +217,10 @@ def make_problem(meta: _Meta, ldc: int, ldcs: int, out_scale_pow2: bool, pow2_sc
         flags |= _ext.MXB_IN_SCALES_POW2
     elif pow2_scales is None:
         flags |= _ext.MXB_IN_SCALES_PROBE
+    if meta.left_col_major:
+        flags |= _ext.MXB_LEFT_COL_MAJOR
+    if meta.right_row_major:
+        flags |= _ext.MXB_RIGHT_ROW_MAJOR
     return MxbProblem(
         meta.m, meta.n, meta.k, meta.sm, meta.sn, meta.sk, meta.qm, meta.qn,
         _DTYPE_CODE[meta.in_dtype], _DTYPE_CODE[meta.out_dtype], _DTYPE_CODE[meta.scale_dtype], flags,
@@ -266,7 +279,9 @@ def mx_gemm_kernel(
     """FP8 micro-scaled GEMM with optional fused group quantisation of the result.
 
     Args follow mxblas/jit_kernels/mx_gemm.py:340-378: ``left`` [M, K] fp8 row-major, ``right``
-    [K, N] fp8 column-major view (``b.T`` of a [N, K] tensor), ``left_scale`` [M/SM, K/SK],
+    [K, N] fp8 column-major view (``b.T`` of a [N, K] tensor) -- the one layout pair the reference has kernels
+    for -- or, beyond the reference, ``left`` column-major (``a.T`` of a [K, M] tensor) and / or ``right``
+    row-major (a [K, N] tensor as stored), ``left_scale`` [M/SM, K/SK],
     ``right_scale`` [K/SK, N/SN] in fp16/bf16/fp32. Returns ``(C, C_scale)``; ``C_scale`` has the
     dtype of the input scales and is a 0-dim empty tensor when ``output_quant`` is False.
 

@@ -114,9 +114,10 @@ def candidates(m: int, n: int, k: int, sk: int, quant: bool, out_transpose: bool
     else:  # scales that change along K: promotion in registers
         for swap in swap_opts:
             if big and sk == 128:
-                for raster in (4, 8, 16, 32):
-                    for tail in (0, 1):
-                        out.append(MxbConfig(256, swap, 8, raster, tail, 0, 2))
+                for bn in (256, 128):
+                    for raster in (4, 8, 16, 32):
+                        for tail in (0, 1):
+                            out.append(MxbConfig(bn, swap, 8, raster, tail, 0, 2))
             for bn, ew in ((128, 4), (128, 8), (256, 8), (64, 4)):
                 for raster in (4, 8, 16):
                     out.append(MxbConfig(bn, swap, ew, raster, 1, 0, 1))

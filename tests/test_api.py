@@ -59,8 +59,16 @@ def test_unsupported_layouts_and_alignment_raise_value_error():
     e4, f32 = torch.float8_e4m3fn, torch.float32
     base = dict(ls=(64, 64), rs=(64, 64))
     # right passed row-major instead of as the column-major view: "No matching template" in the reference
+    # (mxblas/gemm/template.py:70-73); accepted here and flagged for the library
+    meta = get_meta_info(e4, e4, f32, f32, False, None, None, (64, 64), (64, 64), (1, 1), (1, 1), (64, 1), (64, 1),
+                         (1, 1), (1, 1), False, False)
+    assert meta.right_row_major and not meta.left_col_major and meta.ldb == 64
+    meta = get_meta_info(e4, e4, f32, f32, False, None, None, (64, 32), (32, 64), (1, 1), (1, 1), (1, 64), (1, 32),
+                         (1, 1), (1, 1), False, False)
+    assert meta.left_col_major and not meta.right_row_major and meta.lda == 64
+    # a row-major right whose rows are not 16-byte multiples cannot be described to the TMA unit
     with pytest.raises(ValueError):
-        get_meta_info(e4, e4, f32, f32, False, None, None, (64, 64), (64, 64), (1, 1), (1, 1), (64, 1), (64, 1),
+        get_meta_info(e4, e4, f32, f32, False, None, None, (64, 64), (64, 40), (1, 1), (1, 1), (64, 1), (40, 1),
                       (1, 1), (1, 1), False, False)
     # K not a multiple of 16 bytes: the reference exits the process in its TMA encoder; here ValueError
     with pytest.raises(ValueError):

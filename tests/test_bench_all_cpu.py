@@ -33,3 +33,24 @@ def test_rates():
     assert ms == 1.0
     assert abs(tflops - 2 * 1024**3 / 1e-3 / 1e12) < 1e-9
     assert abs(gbs - (1024 * 1024 * 2 + 2 * 1024 * 1024) / 1e-3 / 1e9) < 1e-9
+
+
+def test_sweep_summary_table(tmp_path):
+    """The summary of a sweep CSV: medians per pattern and M, ratio to cuBLASLt, time relative to TT."""
+    import pandas as pd
+
+    from mxblas_b200 import bench_all, plot_box
+
+    path = tmp_path / "sweep.csv"
+    rows = [bench_all.CSV_HEAD]
+    for n, tf_ours, tf_lt in ((4096, 2000.0, 2500.0), (8192, 3000.0, 2800.0)):
+        ms = 2.0 * 1024 * n * 4096 / tf_ours / 1e9
+        rows.append(bench_all.csv_row("m", 1024, n, 4096, 1024, n, 4096, False, 16, "TT", "MXBLAS_B200", ms, tf_ours, 1.0))
+        rows.append(bench_all.csv_row("m", 1024, n, 4096, 1024, n, 4096, False, 16, "TT", "CUBLASLT", ms, tf_lt, 1.0))
+        rows.append(bench_all.csv_row("m", 1024, n, 4096, 1, 128, 128, False, 16, "GB", "MXBLAS_B200", 1.5 * ms, tf_ours / 1.5, 1.0))
+    path.write_text("".join(rows))
+    text = plot_box.summary_table(pd.read_csv(path))
+    tt = [line for line in text.splitlines() if line.startswith("| TT | 1024 |")][0]
+    assert "2500 (2000 .. 3000)" in tt and "| 2650 |" in tt and "| 0.94 |" in tt
+    gb = [line for line in text.splitlines() if line.startswith("| GB | 1024 |")][0]
+    assert "1.50x" in gb and "| - | - |" in gb

@@ -48,9 +48,9 @@ def _worker(rank, world, port):
         per = n // world
         met = orc.compare_hp(loc.cpu().float(), c32[:, rank * per:(rank + 1) * per])
         assert met["max_rel"] <= 1e-2 and met["cosine"] >= 0.9999
-        # the same full result without a collective: each rank's GEMM stores its block into every rank's
-        # symmetric buffer (peer stores from the epilogue); must equal the NCCL-gathered tensor bit for bit.
-        # Quantised results take the all-gather whatever `gather` says.
+        # the same full result without a collective: each rank's GEMM writes its column block of its own symmetric
+        # buffer and a copy kernel (or the copy engines) pushes the block into every other rank's buffer; must equal
+        # the NCCL-gathered tensor bit for bit, for bf16 and for quantised results (codes and scales are pushed)
         out_p, _ = sharded_mx_gemm(*args, gather="peer")
         assert torch.equal(out_p.view(torch.int16), out.view(torch.int16))
         q_p, qs_p = sharded_mx_gemm(*args, True, torch.Size((1, 32)), None, True, True, gather="peer")
@@ -63,6 +63,23 @@ def _worker(rank, world, port):
         out_t, _ = sharded_mx_gemm(*args, False, None, torch.float16, True, gather=True)  # C^T, fp16
         out_tp, _ = sharded_mx_gemm(*args, False, None, torch.float16, True, gather="peer")
         assert out_tp.shape == (n, m) and torch.equal(out_tp.view(torch.int16), out_t.view(torch.int16))
+        # row chunks (the push of one chunk under the GEMM of the next, on a side stream) and both transports
+        m2 = 1024
+        left2, right2, ls2, rs2 = make_inputs(m2, n, k, 1, 1, k, seed=18)
+        args2 = (left2.to(dev), right2.to(dev).t(), ls2.to(dev), rs2.to(dev).t())
+        want2, _ = sharded_mx_gemm(*args2, gather=True)
+        for kw in (dict(peer_chunks=2), dict(peer_chunks=4, peer_transport="dma"), dict(peer_chunks=1, peer_transport="dma")):
+            got2, _ = sharded_mx_gemm(*args2, gather="peer", **kw)
+            assert torch.equal(got2.view(torch.int16), want2.view(torch.int16)), kw
+        q2, qs2 = sharded_mx_gemm(*args2, True, torch.Size((1, 32)), gather=True)
+        q2p, qs2p = sharded_mx_gemm(*args2, True, torch.Size((1, 32)), gather="peer", peer_chunks=2)
+        assert torch.equal(q2p.view(torch.uint8), q2.view(torch.uint8)) and torch.equal(qs2p, qs2)
+        # column blocks that are not 16-byte aligned (N/ranks/QN bf16 scales = 4 bytes per row) take the all-gather
+        left3, right3, ls3, rs3 = make_inputs(256, 64, 128, 256, 64, 128, torch.bfloat16, seed=19)
+        args3 = (left3.to(dev), right3.to(dev).t(), ls3.to(dev), rs3.to(dev).t(), True, torch.Size((1, 16)))
+        q3, qs3 = sharded_mx_gemm(*args3, gather=True)
+        q3p, qs3p = sharded_mx_gemm(*args3, gather="peer")
+        assert torch.equal(q3p.view(torch.uint8), q3.view(torch.uint8)) and torch.equal(qs3p, qs3)
         assert _ext.device_status() == 0
     finally:
         dist.destroy_process_group()

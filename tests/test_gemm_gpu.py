@@ -32,14 +32,17 @@ def dev():
 
 
 def run_case(left, right_phys, ls, rs, quant=False, qn=16, out_dtype=None, out_t=False, cs_t=False,
-             out_pow2=False, pow2_scales=False, config=None, ls_col_major=False, qm=1):
-    """Run the operator on the GPU and the oracle on the CPU; assert the tolerances."""
+             out_pow2=False, pow2_scales=False, config=None, ls_col_major=False, qm=1, left_cm=False, right_rm=False):
+    """Run the operator on the GPU and the oracle on the CPU; assert the tolerances. ``left_cm``: left is passed
+    as the column-major view of a [K, M] tensor; ``right_rm``: right is passed as a row-major [K, N] tensor."""
     d = dev()
     lsd = ls.to(d)
     if ls_col_major:
         lsd = ls.t().contiguous().to(d).t()
+    left_d = left.to(d).t().contiguous().t() if left_cm else left.to(d)
+    right_d = right_phys.to(d).t().contiguous() if right_rm else right_phys.to(d).t()
     out, osc = mxblas.mx_gemm_kernel(
-        left.to(d), right_phys.to(d).t(), lsd, rs.to(d).t(), quant, torch.Size((qm, qn)), out_dtype, out_t, cs_t,
+        left_d, right_d, lsd, rs.to(d).t(), quant, torch.Size((qm, qn)), out_dtype, out_t, cs_t,
         out_scale_pow2=out_pow2, pow2_scales=pow2_scales, config=config,
     )  # fmt: skip
     assert _ext.device_status() == 0, "a kernel recorded a device-side error"
@@ -219,6 +222,45 @@ def test_quant_blocks_2d_large_tiles_and_pairs():
     run_case(*make_inputs(64, 1024, 4096, 1, 1, 4096, seed=306), quant=True, qn=32, qm=16)         # few tiles
     run_case(*make_inputs(2560, 3840, 2048, 1, 1, 2048, seed=307), quant=True, qn=32, qm=32)       # K-sliced last wave
     run_case(*make_inputs(4096, 2560, 256, 1, 1, 256, seed=308), quant=True, qn=32, qm=128, out_t=True, cs_t=True)
+
+
+# ---------------------------------------------------------------------------------------------
+# operand layouts beyond the reference's row-major x column-major (mxblas/gemm/template.py:70-73)
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("left_cm,right_rm", [(False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("pattern", ["TT", "CC", "GB", "BB", "GG32"])
+def test_operand_layouts(pattern, left_cm, right_rm):
+    """NN (row-major right), TN (column-major left, row-major right) and TT (column-major left) operands:
+    the tensor cores read such an operand from shared memory staged along its rows."""
+    m, n, k = 256, 384, 512
+    sm, sn, sk = PATTERNS[pattern](m, n, k)
+    ins = make_inputs(m, n, k, sm, sn, sk, seed=7 + sum(map(ord, pattern)), pow2=pattern == "GG32")
+    kw = dict(left_cm=left_cm, right_rm=right_rm, pow2_scales=True if pattern == "GG32" else False)
+    run_case(*ins, **kw)
+    run_case(*ins, quant=True, qn=32, **kw)
+    run_case(*ins, quant=True, qn=32, out_t=True, cs_t=True, **kw)
+    run_case(*ins, out_t=True, **kw)
+
+
+def test_operand_layouts_large_ragged_and_skinny():
+    both = dict(left_cm=True, right_rm=True)
+    run_case(*make_inputs(4096, 2560, 256, 1, 1, 256, seed=401), right_rm=True)                    # CTA pairs
+    run_case(*make_inputs(4096, 2560, 384, 4096, 2560, 384, torch.bfloat16, seed=402), quant=True, qn=16, **both)
+    run_case(*make_inputs(4096, 2560, 384, 1, 128, 128, seed=403), **both)                         # promotion pairs
+    run_case(*make_inputs(2048, 4096, 512, 1, 1, 32, seed=404, pow2=True), pow2_scales=True, **both)
+    run_case(*make_inputs(208, 336, 272, 1, 1, 272, seed=405), **both)                             # ragged tiles
+    run_case(*make_inputs(208, 336, 272, 1, 1, 272, seed=406), quant=True, qn=16, left_cm=True)
+    run_case(*make_inputs(16, 1024, 4096, 1, 1, 4096, seed=407), right_rm=True)                    # skinny M
+    run_case(*make_inputs(64, 2048, 1024, 1, 1, 1024, seed=408), **both)
+    run_case(*make_inputs(2560, 3840, 2048, 1, 1, 2048, seed=409), right_rm=True)                  # K-sliced last wave
+    # a right operand that is a column slice of a wider row-major tensor (pitch > N)
+    left, right_phys, ls, rs = make_inputs(256, 256, 256, 1, 1, 256, seed=410)
+    d = dev()
+    wide = torch.zeros(256, 512, dtype=torch.uint8, device=d).view(torch.float8_e4m3fn)
+    wide[:, 128:384] = right_phys.to(d).t()
+    out, _ = mxblas.mx_gemm_kernel(left.to(d), wide[:, 128:384], ls.to(d), rs.to(d).t())
+    met = orc.compare_hp(out.cpu().float(), orc.mx_gemm_c32(left, right_phys.t(), ls, rs.t()))
+    assert met["max_rel"] <= HP_MAX_REL and met["cosine"] >= HP_COSINE, met
 
 
 def test_mx_native_and_fallback_agree():
