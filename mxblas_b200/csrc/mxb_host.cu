@@ -341,7 +341,14 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
       // 128 x 256 tiles halve the shared-memory traffic per flop, which bounds the 128 x 128 kernel;
       // they need enough tiles to fill the GPU and have no cross-lane quantisation variant
       const long long tiles256 = static_cast<long long>((pl.rx + 127) / 128) * ((pl.ry + 255) / 256);
-      if (pl.out_mode == OUT_QUANT_X || tiles256 < sms) bn = 128;
+      // ... unless CTA pairs take the problem (decided below): per unit of work the pair kernel promotes
+      // twice as fast as any one-CTA kernel, so it wins even when a quarter of the pairs have a tile
+      // (measured on B200, 4096 x 896 x 7168 with 1x128 . 128x128 scales, 64 pair tiles: 57 us against 98 us
+      // on 224 tiles of 128 x 128)
+      const bool pairs_take_it = q.sk == 128 && pl.out_mode != OUT_QUANT_X && pl.rx >= 256 && !(cfg && cfg->cta_pair == 1) &&
+                                 !(cfg && cfg->splits > 1) && !(grp && grp->block_rows % 256) &&
+                                 static_cast<long long>((pl.rx + 255) / 256) * ((pl.ry + 255) / 256) >= sms / 4;
+      if (pl.out_mode == OUT_QUANT_X || (tiles256 < sms && !pairs_take_it)) bn = 128;
     }
     if (pl.scale_mode == SCALE_MX && bn > 128)
       bn = (pl.out_mode == OUT_QUANT_Y && q.qn > 32) ? 128 : 224;
@@ -393,7 +400,7 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
     // per-channel scales: M = 256 (112 pair tiles) 63.5 us against 71.7 us, M = 512 112.6 against 114.7 us.
     const int pbn = pair_mx ? 224 : bn;
     const long long pair_tiles = static_cast<long long>((pl.rx + 255) / 256) * ((pl.ry + pbn - 1) / pbn);
-    const long long enough = pl.scale_mode == SCALE_EPILOGUE ? sms / 2 : sms;
+    const long long enough = pl.scale_mode == SCALE_EPILOGUE ? sms / 2 : pl.scale_mode == SCALE_PROMOTE ? sms / 4 : sms;
     if (pl.rx >= 256 && pair_tiles >= enough && !(grp && grp->block_rows % 256)) pl.pair = 1;
   }
   if (pl.pair && pair_mx) {

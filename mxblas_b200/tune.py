@@ -194,6 +194,8 @@ def m_bucket(m: int) -> int:
 
 
 def table_key(meta, out_scale_pow2: bool, pow2_scales) -> str:
+    if not (meta.sk == 32 and meta.sm == 1 and meta.sn == 1):
+        pow2_scales = "-"  # only 1x32 scales can take the block-scaled MMA: the flag changes nothing elsewhere
     return "|".join(str(x) for x in (
         meta.in_dtype, meta.out_dtype, meta.scale_dtype, m_bucket(meta.m), meta.n, meta.k, meta.sm if meta.sm == 1 else
         "M" if meta.sm == meta.m else meta.sm, meta.sn, meta.sk, meta.qm, meta.qn, int(meta.out_transpose),
