@@ -365,7 +365,7 @@ def main():
         else:
             pairs = []
             for _ in range(steps):
-                flush_buf.view(torch.int32).sum()
+                flush_buf.view(torch.int32).sum(dtype=torch.int32)
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
                 fn()

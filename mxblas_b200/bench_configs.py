@@ -185,7 +185,7 @@ def dist_main() -> None:
         for it in range(a.iters + 3):
             # evict the operands from L2; the read also keeps the GPU busy while the host enqueues the call,
             # so that no launch latency lands between the events
-            flush.sum()
+            flush.view(torch.int32).sum(dtype=torch.int32)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             dist_mod.sharded_mx_gemm(*args, gather=gather, right_is_local=True, **kw, **peer_kw)

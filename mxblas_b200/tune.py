@@ -63,7 +63,7 @@ def time_call(fn: Callable[[], object], iters: int = 10, warmup: int = 3, flush_
     times = []
     for _ in range(iters):
         if flush_l2:
-            _flush_buf.view(torch.int32).sum()
+            _flush_buf.view(torch.int32).sum(dtype=torch.int32)
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         fn()
