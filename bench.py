@@ -347,10 +347,11 @@ def main():
 
     # Timing rule: a step's inputs must not sit in L2 from the step before. One rank's share of the problem is
     # 200 MiB at N=1 but 81 MiB at N=8, less than the 126 MB L2. So at every N each step is timed by its own pair
-    # of CUDA events on the launching stream and a 256 MiB buffer is read between the steps, outside the pairs
-    # (the read also keeps the GPU busy while the host enqueues the next step, so no launch latency lands inside
-    # a pair). The time of K steps is the sum over the pairs; the K steps are bracketed by barrier + synchronize.
-    flush_buf = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
+    # of CUDA events on the launching stream and a 1 GiB buffer is read between the steps, outside the pairs
+    # (the read, 1 GiB = ~170 us, also keeps the GPU busy while the host enqueues the next step, so no launch
+    # latency lands inside a pair). The time of K steps is the sum over the pairs; the K steps are bracketed by
+    # barrier + synchronize.
+    flush_buf = torch.zeros(1 << 30, dtype=torch.uint8, device=dev)
 
     def timed(fn, steps, flush=True):
         sync_all()
@@ -496,7 +497,7 @@ def main():
         "config": {"workload": WORKLOAD, "global_shape": [M, N, K], "per_gpu_shape": [M, n_local, K],
                    "sharding": f"N-sharded x{world} (each rank its own rows of the [N, K] weight), no collective",
                    "l2": f"operands + outputs = {algo_bytes(n_local) / 2**20:.0f} MiB per step and rank: "
-                         "L2 flushed between the timed steps by a 256 MiB read, each step timed by its own pair of "
+                         "L2 flushed between the timed steps by a 1 GiB read, each step timed by its own pair of "
                          "CUDA events (sum over the steps, max over ranks)"},
         "pct_of_nominal_fp8_peak": 100.0 * value / (NOMINAL_FP8_TFLOPS * world),
         "roofline": roofline, "cpu_baseline": cb, "e2e": e2e, "gpu_launches": int(launches),
