@@ -187,3 +187,38 @@ def test_c_abi_rejects_bad_problems_with_status_codes():
     # null tensors are refused before any CUDA call
     p = _problem(256, 256, 256, 256, 256, 256)
     assert _ext.lib.mxb_gemm(ctypes.byref(p), None, None, None, None, None, None, None, 0, None) == _ext.MXB_ERR_INVALID
+
+
+def test_grouped_gemm_validates_before_touching_the_gpu():
+    """mx_grouped_gemm refuses host tensors and malformed group tables with ValueError (no CPU fallback)."""
+    import mxblas_b200 as mxblas
+
+    a = torch.zeros(128, 64).to(torch.float8_e4m3fn)
+    w = torch.zeros(2, 32, 64).to(torch.float8_e4m3fn)
+    with pytest.raises(ValueError):
+        mxblas.mx_grouped_gemm(a, w.transpose(1, 2), torch.ones(128, 1), torch.ones(2, 32, 1).transpose(1, 2),
+                               torch.zeros(1, dtype=torch.int32))
+
+
+def test_c_abi_layout_flags_and_grouped_plans():
+    """Planner answers for the extensions, without a GPU: operand-layout flags take 128- / 256-wide tiles, a
+    grouped problem refuses what it cannot do."""
+    e4, f32 = torch.float8_e4m3fn, torch.float32
+    meta = get_meta_info(e4, e4, f32, f32, False, None, None, (512, 1024), (1024, 768), (512, 1), (1, 768),
+                         (1024, 1), (768, 1), (1, 1), (768, 1), False, False)
+    assert meta.right_row_major
+    p = make_problem(meta, 768, 0, False, False)
+    cfg = _ext.MxbConfig()
+    assert _ext.lib.mxb_default_config(ctypes.byref(p), ctypes.byref(cfg)) == _ext.MXB_OK
+    assert cfg.bn in (128, 256)
+    nbytes = ctypes.c_size_t(0)
+    plain = make_problem(get_meta_info(e4, e4, f32, f32, False, None, None, (512, 1024), (1024, 768), (512, 1),
+                                       (1, 768), (1024, 1), (1, 1024), (1, 1), (1, 1), False, False), 768, 0, False, False)
+    ok = _ext.lib.mxb_grouped_query_workspace(ctypes.byref(plain), None, 4, 128, ctypes.byref(nbytes))
+    assert ok == _ext.MXB_OK
+    assert _ext.lib.mxb_grouped_query_workspace(ctypes.byref(plain), None, 4, 64, ctypes.byref(nbytes)) == _ext.MXB_ERR_INVALID
+    assert _ext.lib.mxb_grouped_query_workspace(ctypes.byref(plain), None, 0, 128, ctypes.byref(nbytes)) == _ext.MXB_ERR_INVALID
+    pair = _ext.MxbConfig(256, 0, 4, 2, 1, 0, 2)
+    assert _ext.lib.mxb_grouped_query_workspace(ctypes.byref(plain), ctypes.byref(pair), 4, 128, ctypes.byref(nbytes)) == \
+        _ext.MXB_ERR_UNSUPPORTED  # CTA pairs need blocks of whole 256-row tiles
+    assert _ext.lib.mxb_grouped_query_workspace(ctypes.byref(plain), ctypes.byref(pair), 2, 256, ctypes.byref(nbytes)) == _ext.MXB_OK

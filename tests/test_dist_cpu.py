@@ -93,3 +93,21 @@ def test_gather_is_identity_for_one_rank():
         assert torch.equal(gather_columns(x, False), x)
     finally:
         dist.destroy_process_group()
+
+
+def test_peer_row_chunks_rule():
+    """Row chunks of a gather="peer" call: whole 256-row tiles and scale blocks, about 100 us of GEMM or push per
+    chunk, at most 8, none for transposed results."""
+    from mxblas_b200.dist import peer_row_chunks
+
+    big = dict(flops=2.0 * 16384 * 14336 * 8192, push_bytes=16384 * 14336 * 2)       # 1.5 ms of GEMM
+    assert peer_row_chunks(16384, 1, False, False, **big) == 8
+    assert peer_row_chunks(16384, 1, True, False, **big) == 1                          # C^T: column strips
+    assert peer_row_chunks(16384, 1, False, True, **big) == 1
+    small = dict(flops=2.0 * 8192 * 4096 * 8192, push_bytes=8192 * 4096)              # 0.22 ms: two chunks
+    assert peer_row_chunks(8192, 8192, False, False, **small) == 2
+    assert peer_row_chunks(8192, 8192, False, False, flops=1e10, push_bytes=1e6) == 1  # too short to chunk
+    assert peer_row_chunks(8192 + 256, 1, False, False, **big) in (1, 3)               # only divisors that keep 256-row tiles
+    assert peer_row_chunks(16384, 4096, False, False, want=8) == 4                     # chunks hold whole scale blocks
+    push_bound = dict(flops=1e9, push_bytes=7 * 16384 * 3584 * 2)                      # 8 ranks: the push dominates
+    assert peer_row_chunks(16384, 1, False, False, **push_bound) == 8
