@@ -25,6 +25,7 @@ struct KernelEntry {
   int ctas_per_sm;
   int two_per_sm;  // 128-wide tile built as a light CTA (two per SM); narrower tiles are light anyway
   int general;     // also handles operands stored along their rows and grouped GEMMs
+  int single_y;    // promotion with one Y scale per thread's column slice (lean loop)
 };
 
 template <class Cfg>
@@ -47,18 +48,18 @@ cudaError_t launch_kernel(const LaunchArgs& a) {
 #define MXB_ENTRY(BN, SM, OM, EW)                                                              \
   {                                                                                            \
     BN, SM, OM, EW, &launch_kernel<KernelCfg<BN, SM, OM, EW>>, KernelCfg<BN, SM, OM, EW>::SMEM_BYTES, \
-        KernelCfg<BN, SM, OM, EW>::STAGES, KernelCfg<BN, SM, OM, EW>::CTAS_PER_SM, 0, 0          \
+        KernelCfg<BN, SM, OM, EW>::STAGES, KernelCfg<BN, SM, OM, EW>::CTAS_PER_SM, 0, 0, 0       \
   }
 #define MXB_ENTRY_GENERAL(BN, SM, OM, EW)                                                                      \
   {                                                                                                            \
     BN, SM, OM, EW, &launch_kernel<KernelCfg<BN, SM, OM, EW, false, true>>,                                    \
         KernelCfg<BN, SM, OM, EW, false, true>::SMEM_BYTES, KernelCfg<BN, SM, OM, EW, false, true>::STAGES,    \
-        KernelCfg<BN, SM, OM, EW, false, true>::CTAS_PER_SM, 0, 1                                              \
+        KernelCfg<BN, SM, OM, EW, false, true>::CTAS_PER_SM, 0, 1, 0                                           \
   }
 #define MXB_ENTRY_TWO_PER_SM(BN, SM, OM, EW)                                                                 \
   {                                                                                                          \
     BN, SM, OM, EW, &launch_kernel<KernelCfg<BN, SM, OM, EW, true>>, KernelCfg<BN, SM, OM, EW, true>::SMEM_BYTES, \
-        KernelCfg<BN, SM, OM, EW, true>::STAGES, KernelCfg<BN, SM, OM, EW, true>::CTAS_PER_SM, 1, 0          \
+        KernelCfg<BN, SM, OM, EW, true>::STAGES, KernelCfg<BN, SM, OM, EW, true>::CTAS_PER_SM, 1, 0, 0       \
   }
 
 // one table per translation unit

@@ -152,13 +152,15 @@ static const KernelEntry* find_kernel(int bn, int scale_mode, int out_mode, int 
   return nullptr;
 }
 
-static const KernelEntry* find_pair_kernel(int bn, int scale_mode, int out_mode, int epi_warps, int general = 0) {
+static const KernelEntry* find_pair_kernel(int bn, int scale_mode, int out_mode, int epi_warps, int general = 0,
+                                           int single_y = 0) {
   int n = 0;
   const KernelEntry* t = general                    ? general_pair_kernels(&n)
                          : out_mode == OUT_QUANT_2D ? quant2d_pair_kernels(&n)
                                                     : pair_kernels(&n);
   for (int i = 0; i < n; ++i)
-    if (t[i].bn == bn && t[i].scale_mode == scale_mode && t[i].out_mode == out_mode && t[i].epi_warps == epi_warps)
+    if (t[i].bn == bn && t[i].scale_mode == scale_mode && t[i].out_mode == out_mode && t[i].epi_warps == epi_warps &&
+        t[i].single_y == single_y)
       return &t[i];
   return nullptr;
 }
@@ -231,6 +233,16 @@ static int light128_override() {
     v = e == nullptr ? -1 : (e[0] == '1' ? 1 : 0);
   }
   return v;
+}
+
+// MXBLAS_B200_SINGLE_Y=0 keeps promotion on the general loop (measurement aid)
+static bool single_y_disabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("MXBLAS_B200_SINGLE_Y");
+    v = (e != nullptr && e[0] == '0') ? 1 : 0;
+  }
+  return v == 1;
 }
 
 static int pick_bn(int ry) { return ry <= 32 ? 32 : ry <= 64 ? 64 : ry <= 128 ? 128 : 256; }
@@ -416,7 +428,14 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
     const int env = light128_override();
     if (env == 1 || (env < 0 && t128 > sms)) two_per_sm = 1;
   }
-  pl.kernel = pl.pair ? find_pair_kernel(bn, pl.scale_mode, pl.out_mode, ew, general)
+  // promotion on CTA pairs: the lean loop where one Y scale covers a thread's whole column slice
+  int single_y = 0;
+  if (pl.pair && pl.scale_mode == SCALE_PROMOTE && ew == 8 && !((general || q2d) && bn != 256)) {
+    const int gy = swap ? q.sm : q.sn;
+    const int slice_cols = bn / 2;
+    if (gy % slice_cols == 0 && !single_y_disabled()) single_y = 1;
+  }
+  pl.kernel = pl.pair ? find_pair_kernel(bn, pl.scale_mode, pl.out_mode, ew, general, single_y)
                       : find_kernel(bn, pl.scale_mode, pl.out_mode, ew, two_per_sm, general);
   if (pl.kernel == nullptr) return MXB_ERR_UNSUPPORTED;
   if (pl.out_mode == OUT_QUANT_Y || q2d) {

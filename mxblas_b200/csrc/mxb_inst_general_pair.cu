@@ -7,9 +7,16 @@ namespace mxb {
 #define MXB_PAIR_ENTRY_GENERAL(BN, SM, OM, EW)                                                         \
   {                                                                                                    \
     BN, SM, OM, EW, &launch_pair_kernel<PairCfg<BN, SM, OM, EW, true>>,                                \
-        PairCfg<BN, SM, OM, EW, true>::SMEM_BYTES, PairCfg<BN, SM, OM, EW, true>::STAGES, 1, 0, 1      \
+        PairCfg<BN, SM, OM, EW, true>::SMEM_BYTES, PairCfg<BN, SM, OM, EW, true>::STAGES, 1, 0, 1, 0   \
+  }
+#define MXB_PAIR_ENTRY_GENERAL_SINGLE_Y(BN, SM, OM, EW)                                                        \
+  {                                                                                                           \
+    BN, SM, OM, EW, &launch_pair_kernel<PairCfg<BN, SM, OM, EW, true, true>>,                                 \
+        PairCfg<BN, SM, OM, EW, true, true>::SMEM_BYTES, PairCfg<BN, SM, OM, EW, true, true>::STAGES, 1, 0, 1, 1 \
   }
 static const KernelEntry kGeneralPair[] = {
+    MXB_PAIR_ENTRY_GENERAL_SINGLE_Y(256, SCALE_PROMOTE, OUT_HP, 8),
+    MXB_PAIR_ENTRY_GENERAL_SINGLE_Y(256, SCALE_PROMOTE, OUT_QUANT_Y, 8),
     MXB_PAIR_ENTRY_GENERAL(256, SCALE_EPILOGUE, OUT_HP, 4),      MXB_PAIR_ENTRY_GENERAL(256, SCALE_EPILOGUE, OUT_QUANT_Y, 4),
     MXB_PAIR_ENTRY_GENERAL(256, SCALE_EPILOGUE, OUT_QUANT_Y, 8), MXB_PAIR_ENTRY_GENERAL(256, SCALE_EPILOGUE, OUT_QUANT_X, 4),
     MXB_PAIR_ENTRY_GENERAL(256, SCALE_EPILOGUE, OUT_QUANT_X, 8), MXB_PAIR_ENTRY_GENERAL(256, SCALE_PROMOTE, OUT_HP, 8),

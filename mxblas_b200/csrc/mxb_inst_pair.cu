@@ -8,9 +8,17 @@ namespace mxb {
 #define MXB_PAIR_ENTRY(BN, SM, OM, EW)                                                                    \
   {                                                                                                       \
     BN, SM, OM, EW, &launch_pair_kernel<PairCfg<BN, SM, OM, EW>>, PairCfg<BN, SM, OM, EW>::SMEM_BYTES,    \
-        PairCfg<BN, SM, OM, EW>::STAGES, 1, 0, 0                                                          \
+        PairCfg<BN, SM, OM, EW>::STAGES, 1, 0, 0, 0                                                       \
+  }
+// single-scale twins of the promotion kernels (one Y scale per thread's column slice)
+#define MXB_PAIR_ENTRY_SINGLE_Y(BN, SM, OM, EW)                                                                   \
+  {                                                                                                               \
+    BN, SM, OM, EW, &launch_pair_kernel<PairCfg<BN, SM, OM, EW, false, true>>,                                    \
+        PairCfg<BN, SM, OM, EW, false, true>::SMEM_BYTES, PairCfg<BN, SM, OM, EW, false, true>::STAGES, 1, 0, 0, 1 \
   }
 static const KernelEntry kPair[] = {
+    MXB_PAIR_ENTRY_SINGLE_Y(256, SCALE_PROMOTE, OUT_HP, 8), MXB_PAIR_ENTRY_SINGLE_Y(256, SCALE_PROMOTE, OUT_QUANT_Y, 8),
+    MXB_PAIR_ENTRY_SINGLE_Y(128, SCALE_PROMOTE, OUT_HP, 8), MXB_PAIR_ENTRY_SINGLE_Y(128, SCALE_PROMOTE, OUT_QUANT_Y, 8),
     MXB_PAIR_ENTRY(256, SCALE_EPILOGUE, OUT_HP, 4),      MXB_PAIR_ENTRY(256, SCALE_EPILOGUE, OUT_HP, 8),
     MXB_PAIR_ENTRY(256, SCALE_EPILOGUE, OUT_QUANT_Y, 4), MXB_PAIR_ENTRY(256, SCALE_EPILOGUE, OUT_QUANT_Y, 8),
     MXB_PAIR_ENTRY(256, SCALE_EPILOGUE, OUT_QUANT_X, 4), MXB_PAIR_ENTRY(256, SCALE_EPILOGUE, OUT_QUANT_X, 8),

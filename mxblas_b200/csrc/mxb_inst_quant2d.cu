@@ -18,9 +18,12 @@ const KernelEntry* quant2d_kernels(int* count) {
 #define MXB_PAIR_ENTRY(BN, SM, OM, EW)                                                                    \
   {                                                                                                       \
     BN, SM, OM, EW, &launch_pair_kernel<PairCfg<BN, SM, OM, EW>>, PairCfg<BN, SM, OM, EW>::SMEM_BYTES,    \
-        PairCfg<BN, SM, OM, EW>::STAGES, 1, 0, 0                                                          \
+        PairCfg<BN, SM, OM, EW>::STAGES, 1, 0, 0, 0                                                       \
   }
 static const KernelEntry kQuant2dPair[] = {
+    {256, SCALE_PROMOTE, OUT_QUANT_2D, 8, &launch_pair_kernel<PairCfg<256, SCALE_PROMOTE, OUT_QUANT_2D, 8, false, true>>,
+     PairCfg<256, SCALE_PROMOTE, OUT_QUANT_2D, 8, false, true>::SMEM_BYTES,
+     PairCfg<256, SCALE_PROMOTE, OUT_QUANT_2D, 8, false, true>::STAGES, 1, 0, 0, 1},  // single-scale twin
     MXB_PAIR_ENTRY(256, SCALE_EPILOGUE, OUT_QUANT_2D, 8),
     MXB_PAIR_ENTRY(256, SCALE_PROMOTE, OUT_QUANT_2D, 8),
     MXB_PAIR_ENTRY(224, SCALE_MX, OUT_QUANT_2D, 4),

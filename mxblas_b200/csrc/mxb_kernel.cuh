@@ -118,6 +118,7 @@ struct KernelCfg {
   static constexpr int SCALE_MODE = SCALE_MODE_;
   static constexpr int OUT_MODE = OUT_MODE_;
   static constexpr int EPI_WARPS = EPI_WARPS_;
+  static constexpr bool SINGLE_Y = false;  // (CTA-pair promotion kernels have single-scale twins, see PairCfg)
   // warp 0 = TMA producer, warp 1 = MMA issuer. With eight epilogue warps the two control warps
   // are padded to a full warpgroup so that registers can be moved from it to the epilogue
   // warpgroups (setmaxnreg); a 320-thread CTA would be capped at 168 registers per thread anyway.
@@ -749,6 +750,91 @@ __device__ __forceinline__ bool promote_groups(const GemmParams& p, float (&acc)
     }
     ++acc_it;
     scales_end(gi);
+  }
+  return ok;
+}
+
+// The same loop for the common case that ONE Y scale covers a thread's whole column slice (128 x 128 weight
+// blocks under 128- or 64-column slices): no per-lane scale batches and shuffles, no shared-memory stage, one
+// scale product per group. It exists as instantiations of its own (Cfg::SINGLE_Y), never beside the general
+// loop in one kernel: the promotion warps sit at their register limit, this loop reacts to register pressure
+// out of proportion, and what counts is the larger of the two. Measured on B200 (4096 x 7168 x 7168, 1x128 .
+// 128x128 scales, CTA pairs): 313 us with the general loop, 452 us with both loops in the kernel and this one
+// taken, 257 us with this loop alone.
+template <class Cfg, class WaitFn, class PeekFn, class ReleaseFn>
+__device__ __forceinline__ bool promote_groups_single_y(const GemmParams& p, float (&acc)[Cfg::COLS_PER_THREAD],
+                                                        int xrow, int ycol0, int kbeg, int kend, int lane,
+                                                        uint32_t ta_base, uint32_t& acc_it, long long sy_goff,
+                                                        WaitFn wait_group, PeekFn peek_group, ReleaseFn release_group) {
+  bool ok = true;
+  const int ngroups = (kend - kbeg + p.gk - 1) / p.gk;
+  const int g0 = kbeg / p.gk;
+  const int nvalid = min(ngroups, p.k / p.gk - g0);
+  const int dt = p.scale_dtype;
+  const long long sx_row = (xrow < p.rx ? (xrow / p.gx) * p.sx_rs : 0) + static_cast<long long>(g0) * p.sx_ks;
+  const long long sy_row = sy_goff + (ycol0 < p.ry ? (ycol0 / p.gy) * p.sy_rs : 0) + static_cast<long long>(g0) * p.sy_ks;
+  const int last = nvalid - 1;
+  auto fetch = [&](int gi, float& sx, float& sy) {
+    const int g = min(gi, last);
+    sx = load_scale(p.sx, sx_row + g * p.sx_ks, dt);
+    sy = load_scale(p.sy, sy_row + g * p.sy_ks, dt);
+  };
+  float sx0, sy0, sx1, sy1, sx2 = 0.f, sy2 = 0.f;
+  fetch(0, sx0, sy0);
+  fetch(1, sx1, sy1);
+  bool next_ready = false;
+#pragma unroll 1
+  for (int gi = 0; gi < ngroups; ++gi) {
+    fetch(gi + 2, sx2, sy2);
+    const uint32_t b = acc_it % Cfg::NUM_ACC;
+    uint32_t okw = 1u;
+    if (lane == 0) okw = (next_ready || wait_group(acc_it)) ? 1u : 0u;
+    okw = __shfl_sync(0xffffffffu, okw, 0);
+    if (okw == 0u) {
+      ok = false;
+      break;
+    }
+    tc_fence_after();
+    const uint32_t ta = ta_base + b * Cfg::ACC_STRIDE;
+    const float sc = sx0 * sy0;
+    auto chunk = [&](const uint32_t (&r)[32], int c) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) fma2(acc[c * 32 + i], acc[c * 32 + i + 1], r[i], r[i + 1], sc, sc);
+    };
+    uint32_t r0[32], r1[32];
+    __syncwarp();
+    tmem_ld_32x32(ta, r0);
+    tmem_ld_32x32(ta + 32, r1);
+    tmem_ld_wait();
+    if constexpr (Cfg::CHUNKS == 2) {
+      tc_fence_before();
+      __syncwarp();
+      release_group(b);
+      if (lane == 0) next_ready = peek_group(acc_it + 1);
+      chunk(r0, 0);
+      chunk(r1, 1);
+    } else {
+      static_assert(Cfg::CHUNKS == 2 || Cfg::CHUNKS == 4, "single-scale promotion: 64- or 128-column slices");
+      chunk(r0, 0);
+      __syncwarp();
+      tmem_ld_32x32(ta + 64, r0);
+      chunk(r1, 1);
+      tmem_ld_wait();
+      __syncwarp();
+      tmem_ld_32x32(ta + 96, r1);
+      chunk(r0, 2);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      release_group(b);
+      if (lane == 0) next_ready = peek_group(acc_it + 1);
+      chunk(r1, 3);
+    }
+    ++acc_it;
+    sx0 = sx1;
+    sy0 = sy1;
+    sx1 = sx2;
+    sy1 = sy2;
   }
   return ok;
 }

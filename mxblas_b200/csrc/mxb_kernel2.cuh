@@ -39,9 +39,13 @@ namespace mxb {
 // next to the two accumulator buffers; with scales constant along K the narrower tile exists as a
 // configuration: the MMAs are bound by shared-memory traffic, which shrinks by 6 % only, so saving a wave of
 // tiles with it measured no faster). Each CTA stages BN/2 rows of Y.
-template <int BN_, int SCALE_MODE_, int OUT_MODE_, int EPI_WARPS_, bool GENERAL_ = false>
+// SINGLE_Y_ (promotion only): every thread's column slice lies inside one scale block of Y (128 x 128 weight
+// blocks): the lean loop promote_groups_single_y replaces the general one.
+template <int BN_, int SCALE_MODE_, int OUT_MODE_, int EPI_WARPS_, bool GENERAL_ = false, bool SINGLE_Y_ = false>
 struct PairCfg {
   static constexpr bool GENERAL = GENERAL_;  // operands stored along their rows and grouped GEMMs (see KernelCfg)
+  static constexpr bool SINGLE_Y = SINGLE_Y_;
+  static_assert(!SINGLE_Y_ || SCALE_MODE_ == SCALE_PROMOTE, "single-scale twins exist for promotion only");
   static constexpr int BN = BN_;
   static constexpr int BM_PAIR = 256;      // rows of the pair's tile (each CTA owns 128)
   static constexpr int SCALE_MODE = SCALE_MODE_;
@@ -419,19 +423,23 @@ mx_gemm_sm100_pair(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 #pragma unroll
         for (int j = 0; j < Cfg::COLS_PER_THREAD; ++j) acc[j] = 0.f;
         const uint32_t tempty0 = map_to_cta(bar_tempty, 0);
-        ok = promote_groups<Cfg>(
-            p, acc, xrow, ycol0, un.kb0 * 128, un.kb1 * 128, e, lane,
-            tmem_base + lane_addr + slice * Cfg::COLS_PER_THREAD, acc_it, sYs, sy_goff,
-            // partial sum number `it` of this CTA is complete when the commit of its K block arrives on the
-            // stage's empty barrier: stage it % STAGES, turn it / STAGES
-            [&](uint32_t it) {
-              return mbar_wait(bar_empty + 8 * (it % STAGES), (it / STAGES) & 1, abort_flag, p.status,
-                               DEV_TIMEOUT_EPILOGUE);
-            },
-            [&](uint32_t it) { return mbar_test_wait(bar_empty + 8 * (it % STAGES), (it / STAGES) & 1); },
-            [&](uint32_t b) {
-              if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * b);
-            });
+        // partial sum number `it` of this CTA is complete when the commit of its K block arrives on the stage's
+        // empty barrier: stage it % STAGES, turn it / STAGES
+        auto wait_fn = [&](uint32_t it) {
+          return mbar_wait(bar_empty + 8 * (it % STAGES), (it / STAGES) & 1, abort_flag, p.status,
+                           DEV_TIMEOUT_EPILOGUE);
+        };
+        auto peek_fn = [&](uint32_t it) { return mbar_test_wait(bar_empty + 8 * (it % STAGES), (it / STAGES) & 1); };
+        auto release_fn = [&](uint32_t b) {
+          if (lane == 0) mbar_arrive_cluster(tempty0 + 8 * b);
+        };
+        const uint32_t ta0 = tmem_base + lane_addr + slice * Cfg::COLS_PER_THREAD;
+        if constexpr (Cfg::SINGLE_Y)
+          ok = promote_groups_single_y<Cfg>(p, acc, xrow, ycol0, un.kb0 * 128, un.kb1 * 128, lane, ta0, acc_it,
+                                            sy_goff, wait_fn, peek_fn, release_fn);
+        else
+          ok = promote_groups<Cfg>(p, acc, xrow, ycol0, un.kb0 * 128, un.kb1 * 128, e, lane, ta0, acc_it, sYs,
+                                   sy_goff, wait_fn, peek_fn, release_fn);
         if (!ok) break;
         if (un.whole) {
           OutputStage<Cfg, SRC_REGS> os{p, acc, 0u, 1.f, nullptr, xrow, ycol0, lane, quad,
