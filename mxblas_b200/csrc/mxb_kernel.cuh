@@ -771,13 +771,15 @@ __device__ __forceinline__ bool promote_groups_single_y(const GemmParams& p, flo
   const int g0 = kbeg / p.gk;
   const int nvalid = min(ngroups, p.k / p.gk - g0);
   const int dt = p.scale_dtype;
-  const long long sx_row = (xrow < p.rx ? (xrow / p.gx) * p.sx_rs : 0) + static_cast<long long>(g0) * p.sx_ks;
-  const long long sy_row = sy_goff + (ycol0 < p.ry ? (ycol0 / p.gy) * p.sy_rs : 0) + static_cast<long long>(g0) * p.sy_ks;
+  // (32-bit element indices: a scale tensor has far fewer than 2^31 elements, and every register counts here)
+  const int sx_row = static_cast<int>((xrow < p.rx ? (xrow / p.gx) * p.sx_rs : 0) + static_cast<long long>(g0) * p.sx_ks);
+  const int sy_row = static_cast<int>(sy_goff + (ycol0 < p.ry ? (ycol0 / p.gy) * p.sy_rs : 0) + static_cast<long long>(g0) * p.sy_ks);
+  const int sx_ks = static_cast<int>(p.sx_ks), sy_ks = static_cast<int>(p.sy_ks);
   const int last = nvalid - 1;
   auto fetch = [&](int gi, float& sx, float& sy) {
     const int g = min(gi, last);
-    sx = load_scale(p.sx, sx_row + g * p.sx_ks, dt);
-    sy = load_scale(p.sy, sy_row + g * p.sy_ks, dt);
+    sx = load_scale(p.sx, sx_row + g * sx_ks, dt);
+    sy = load_scale(p.sy, sy_row + g * sy_ks, dt);
   };
   float sx0, sy0, sx1, sy1, sx2 = 0.f, sy2 = 0.f;
   fetch(0, sx0, sy0);
