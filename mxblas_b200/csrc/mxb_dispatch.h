@@ -56,6 +56,12 @@ cudaError_t launch_kernel(const LaunchArgs& a) {
         KernelCfg<BN, SM, OM, EW, false, true>::SMEM_BYTES, KernelCfg<BN, SM, OM, EW, false, true>::STAGES,    \
         KernelCfg<BN, SM, OM, EW, false, true>::CTAS_PER_SM, 0, 1, 0                                           \
   }
+#define MXB_ENTRY_SINGLE_Y(BN, SM, OM, EW, GEN)                                                                          \
+  {                                                                                                                    \
+    BN, SM, OM, EW, &launch_kernel<KernelCfg<BN, SM, OM, EW, false, GEN, true>>,                                       \
+        KernelCfg<BN, SM, OM, EW, false, GEN, true>::SMEM_BYTES, KernelCfg<BN, SM, OM, EW, false, GEN, true>::STAGES,  \
+        KernelCfg<BN, SM, OM, EW, false, GEN, true>::CTAS_PER_SM, 0, GEN ? 1 : 0, 1                                    \
+  }
 #define MXB_ENTRY_TWO_PER_SM(BN, SM, OM, EW)                                                                 \
   {                                                                                                          \
     BN, SM, OM, EW, &launch_kernel<KernelCfg<BN, SM, OM, EW, true>>, KernelCfg<BN, SM, OM, EW, true>::SMEM_BYTES, \

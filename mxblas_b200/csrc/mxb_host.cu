@@ -138,7 +138,7 @@ static int operand_map(const void* ptr, long long rows, long long k, long long p
 // kernel table
 // ---------------------------------------------------------------------------------------------
 static const KernelEntry* find_kernel(int bn, int scale_mode, int out_mode, int epi_warps, int two_per_sm = 0,
-                                      int general = 0) {
+                                      int general = 0, int single_y = 0) {
   int n = 0;
   const KernelEntry* t = general                       ? general_kernels(&n)
                          : out_mode == OUT_QUANT_2D    ? quant2d_kernels(&n)
@@ -147,7 +147,7 @@ static const KernelEntry* find_kernel(int bn, int scale_mode, int out_mode, int 
                                                         : mx_kernels(&n);
   for (int i = 0; i < n; ++i)
     if (t[i].bn == bn && t[i].scale_mode == scale_mode && t[i].out_mode == out_mode && t[i].epi_warps == epi_warps &&
-        t[i].two_per_sm == two_per_sm)
+        t[i].two_per_sm == two_per_sm && t[i].single_y == single_y)
       return &t[i];
   return nullptr;
 }
@@ -435,8 +435,19 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
     const int slice_cols = bn / 2;
     if (gy % slice_cols == 0 && !single_y_disabled()) single_y = 1;
   }
+  // (one-CTA promotion kernels: twins exist for 128-wide tiles with [1, QN] groups or 16-bit results; on
+  // 256-wide one-CTA tiles the lean loop measured slower than the general one: 1184 against 754 us on a
+  // grouped 16384 x 4096 x 7168 problem)
+  if (!pl.pair && pl.scale_mode == SCALE_PROMOTE && !q2d && pl.out_mode != OUT_QUANT_X && bn == 128 &&
+      !(general && ew != 8) && !single_y_disabled()) {
+    const int gy = swap ? q.sm : q.sn;
+    if (gy % (bn / (ew / 4)) == 0) single_y = 1;
+  }
   pl.kernel = pl.pair ? find_pair_kernel(bn, pl.scale_mode, pl.out_mode, ew, general, single_y)
-                      : find_kernel(bn, pl.scale_mode, pl.out_mode, ew, two_per_sm, general);
+                      : find_kernel(bn, pl.scale_mode, pl.out_mode, ew, two_per_sm, general, single_y);
+  if (pl.kernel == nullptr && single_y)  // no lean twin of this shape: the general loop
+    pl.kernel = pl.pair ? find_pair_kernel(bn, pl.scale_mode, pl.out_mode, ew, general, 0)
+                        : find_kernel(bn, pl.scale_mode, pl.out_mode, ew, two_per_sm, general, 0);
   if (pl.kernel == nullptr) return MXB_ERR_UNSUPPORTED;
   if (pl.out_mode == OUT_QUANT_Y || q2d) {
     const int cols = bn / (ew / 4);

@@ -15,6 +15,8 @@ static const KernelEntry kGeneral[] = {
     MXB_ENTRY_GENERAL(256, SCALE_PROMOTE, OUT_HP, 8),       MXB_ENTRY_GENERAL(256, SCALE_PROMOTE, OUT_QUANT_Y, 8),
     MXB_ENTRY_GENERAL(128, SCALE_MX, OUT_HP, 4),            MXB_ENTRY_GENERAL(128, SCALE_MX, OUT_QUANT_Y, 4),
     MXB_ENTRY_GENERAL(128, SCALE_MX, OUT_QUANT_X, 4),
+    // single-scale twins of the promotion kernels (lean loop)
+    MXB_ENTRY_SINGLE_Y(128, SCALE_PROMOTE, OUT_HP, 8, true),       MXB_ENTRY_SINGLE_Y(128, SCALE_PROMOTE, OUT_QUANT_Y, 8, true),
 };
 const KernelEntry* general_kernels(int* count) {
   *count = static_cast<int>(sizeof(kGeneral) / sizeof(kGeneral[0]));

@@ -110,15 +110,19 @@ __device__ __forceinline__ float group_scale(float amax, float inv_fp8_max, int 
 // GENERAL_: the instantiation also handles operands stored along their rows (column-major left, row-major
 // right) and grouped GEMMs. The plain instantiations compile those paths out: as run-time branches they cost
 // the kernels of the reference's own layout 4 % (same-box A/B on B200: 8192^3 per-tensor 364.5 -> 380 us).
-template <int BN_, int SCALE_MODE_, int OUT_MODE_, int EPI_WARPS_, bool TWO_PER_SM_ = false, bool GENERAL_ = false>
+// SINGLE_Y_ (promotion only): every thread's column slice lies inside one scale block of Y, and the lean loop
+// promote_groups_single_y replaces the general one.
+template <int BN_, int SCALE_MODE_, int OUT_MODE_, int EPI_WARPS_, bool TWO_PER_SM_ = false, bool GENERAL_ = false,
+          bool SINGLE_Y_ = false>
 struct KernelCfg {
   static constexpr bool GENERAL = GENERAL_;
+  static constexpr bool SINGLE_Y = SINGLE_Y_;
+  static_assert(!SINGLE_Y_ || SCALE_MODE_ == SCALE_PROMOTE, "single-scale twins exist for promotion only");
   static constexpr int BM = 128, BK = 128;
   static constexpr int BN = BN_;
   static constexpr int SCALE_MODE = SCALE_MODE_;
   static constexpr int OUT_MODE = OUT_MODE_;
   static constexpr int EPI_WARPS = EPI_WARPS_;
-  static constexpr bool SINGLE_Y = false;  // (CTA-pair promotion kernels have single-scale twins, see PairCfg)
   // warp 0 = TMA producer, warp 1 = MMA issuer. With eight epilogue warps the two control warps
   // are padded to a full warpgroup so that registers can be moved from it to the epilogue
   // warpgroups (setmaxnreg); a 320-thread CTA would be capped at 168 registers per thread anyway.
@@ -1130,17 +1134,21 @@ mx_gemm_sm100(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
 #pragma unroll
         for (int j = 0; j < Cfg::COLS_PER_THREAD; ++j) acc[j] = 0.f;
         // K range padded to whole blocks: the MMA warp closes a buffer per group
-        ok = promote_groups<Cfg>(
-            p, acc, xrow, ycol0, kb0 * 128, kb1 * 128, e, lane,
-            tmem_base + lane_addr + slice * Cfg::COLS_PER_THREAD, acc_it, sYs, sy_goff,
-            [&](uint32_t it) {
-              return mbar_wait(bar_tfull + 8 * (it % NUM_ACC), (it / NUM_ACC) & 1, abort_flag, p.status,
-                               DEV_TIMEOUT_EPILOGUE);
-            },
-            [&](uint32_t it) { return mbar_test_wait(bar_tfull + 8 * (it % NUM_ACC), (it / NUM_ACC) & 1); },
-            [&](uint32_t b) {
-              if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
-            });
+        auto wait_fn = [&](uint32_t it) {
+          return mbar_wait(bar_tfull + 8 * (it % NUM_ACC), (it / NUM_ACC) & 1, abort_flag, p.status,
+                           DEV_TIMEOUT_EPILOGUE);
+        };
+        auto peek_fn = [&](uint32_t it) { return mbar_test_wait(bar_tfull + 8 * (it % NUM_ACC), (it / NUM_ACC) & 1); };
+        auto release_fn = [&](uint32_t b) {
+          if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
+        };
+        const uint32_t ta0 = tmem_base + lane_addr + slice * Cfg::COLS_PER_THREAD;
+        if constexpr (Cfg::SINGLE_Y)
+          ok = promote_groups_single_y<Cfg>(p, acc, xrow, ycol0, kb0 * 128, kb1 * 128, lane, ta0, acc_it, sy_goff,
+                                            wait_fn, peek_fn, release_fn);
+        else
+          ok = promote_groups<Cfg>(p, acc, xrow, ycol0, kb0 * 128, kb1 * 128, e, lane, ta0, acc_it, sYs, sy_goff,
+                                   wait_fn, peek_fn, release_fn);
         if (!ok) break;
         if (splits == 1) {
           OutputStage<Cfg, SRC_REGS> os{p, acc, 0u, 1.f, nullptr, xrow, ycol0, lane, quad,
