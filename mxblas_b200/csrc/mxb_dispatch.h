@@ -52,20 +52,20 @@ cudaError_t launch_kernel(const LaunchArgs& a) {
   }
 #define MXB_ENTRY_GENERAL(BN, SM, OM, EW)                                                                      \
   {                                                                                                            \
-    BN, SM, OM, EW, &launch_kernel<KernelCfg<BN, SM, OM, EW, false, true>>,                                    \
-        KernelCfg<BN, SM, OM, EW, false, true>::SMEM_BYTES, KernelCfg<BN, SM, OM, EW, false, true>::STAGES,    \
-        KernelCfg<BN, SM, OM, EW, false, true>::CTAS_PER_SM, 0, 1, 0                                           \
+    BN, SM, OM, EW, &launch_kernel<KernelCfg<BN, SM, OM, EW, 0, true>>,                                        \
+        KernelCfg<BN, SM, OM, EW, 0, true>::SMEM_BYTES, KernelCfg<BN, SM, OM, EW, 0, true>::STAGES,            \
+        KernelCfg<BN, SM, OM, EW, 0, true>::CTAS_PER_SM, 0, 1, 0                                               \
   }
 #define MXB_ENTRY_SINGLE_Y(BN, SM, OM, EW, GEN)                                                                          \
   {                                                                                                                    \
-    BN, SM, OM, EW, &launch_kernel<KernelCfg<BN, SM, OM, EW, false, GEN, true>>,                                       \
-        KernelCfg<BN, SM, OM, EW, false, GEN, true>::SMEM_BYTES, KernelCfg<BN, SM, OM, EW, false, GEN, true>::STAGES,  \
-        KernelCfg<BN, SM, OM, EW, false, GEN, true>::CTAS_PER_SM, 0, GEN ? 1 : 0, 1                                    \
+    BN, SM, OM, EW, &launch_kernel<KernelCfg<BN, SM, OM, EW, 0, GEN, true>>,                                           \
+        KernelCfg<BN, SM, OM, EW, 0, GEN, true>::SMEM_BYTES, KernelCfg<BN, SM, OM, EW, 0, GEN, true>::STAGES,          \
+        KernelCfg<BN, SM, OM, EW, 0, GEN, true>::CTAS_PER_SM, 0, GEN ? 1 : 0, 1                                        \
   }
-#define MXB_ENTRY_TWO_PER_SM(BN, SM, OM, EW)                                                                 \
-  {                                                                                                          \
-    BN, SM, OM, EW, &launch_kernel<KernelCfg<BN, SM, OM, EW, true>>, KernelCfg<BN, SM, OM, EW, true>::SMEM_BYTES, \
-        KernelCfg<BN, SM, OM, EW, true>::STAGES, KernelCfg<BN, SM, OM, EW, true>::CTAS_PER_SM, 1, 0, 0       \
+#define MXB_ENTRY_TWO_PER_SM(BN, SM, OM, EW)                                                           \
+  {                                                                                                    \
+    BN, SM, OM, EW, &launch_kernel<KernelCfg<BN, SM, OM, EW, 1>>, KernelCfg<BN, SM, OM, EW, 1>::SMEM_BYTES, \
+        KernelCfg<BN, SM, OM, EW, 1>::STAGES, KernelCfg<BN, SM, OM, EW, 1>::CTAS_PER_SM, 1, 0, 0       \
   }
 
 // one table per translation unit

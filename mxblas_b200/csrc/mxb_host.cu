@@ -314,29 +314,42 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
   const bool cross_warp_quant = (pl.out_mode == OUT_QUANT_X && q.qn > 32) || (q2d && pl.qx > 32);
 
   // Skinny problems whose 128-row tiles alone cannot occupy the GPU (a decode step against a weight of a few
-  // thousand rows): narrow Y tiles on the two-CTA-per-SM kernels and a split K, chosen to bring the number of
-  // units as close to the 2 x SMs resident CTAs as it gets. Ties go to the smaller split (its exchange costs
-  // a few microseconds), then to the wider tile. Measured on B200 over M = 16..128 x N = 2048..16384: 1.2-2.2x
-  // faster than one 128-wide tile per row block with ctas / tiles splits.
+  // thousand rows): the tile width along Y and the K split are chosen by a cost estimate. What it knows, all
+  // measured on B200 with the timeline of a 128 x 8192 x 8192 call:
+  //  * one MMA thread issues a 128-deep K block in ~0.37 us whatever the tile width, and two CTAs on one SM do
+  //    not slow each other down: a unit's K loop costs 0.37 us per K block, so the work is cut into as many
+  //    units as there are slots (light CTAs: two per SM), unless the weight's bytes / 5.5 TB/s take longer;
+  //  * a second round of units costs its K loop again plus ~3 us;
+  //  * the split-K exchange costs ~3 us (park, fence, count) plus ~0.5 us per 32 KiB slice the last unit adds up;
+  //  * the output stage costs ~0.7 us per 32 columns of the tile.
+  // Measured over M = 16..128, N = 4096..10240, K = 7168..28672: within 10 % of the best of all candidates.
   int skinny_bn = 0, skinny_splits = 0;
   {
     const int x_tiles = (pl.rx + 127) / 128, kblocks = (q.k + 127) / 128;
     const bool free_choice = !(cfg && (cfg->bn > 0 || cfg->splits > 0 || cfg->cta_pair == 2 || cfg->ctas > 0)) && !general;
     const bool split_ok = !cross_warp_quant;
     if (free_choice && swap && pl.scale_mode == SCALE_EPILOGUE && pl.ry <= 128 && x_tiles < sms && split_ok && !grp) {
-      const int slots = 2 * sms;
-      long long best_units = 0;
-      for (int bn_try = 64; bn_try >= 32; bn_try /= 2) {
-        if (bn_try == 64 && pl.ry <= 32) continue;
+      double best_us = 1e30;
+      for (int bn_try = 128; bn_try >= 32; bn_try /= 2) {
+        if (bn_try > 32 && bn_try >= 2 * pl.ry) continue;  // more than half of the tile would be padding
         if (pl.out_mode == OUT_QUANT_Y && bn_try % q.qn) continue;
+        if (bn_try == 128 && q2d) continue;
         const int y_tiles = (pl.ry + bn_try - 1) / bn_try;
         for (int sp = 1; sp <= 8; sp *= 2) {
           if (sp > 1 && kblocks / sp < 8) break;
           const long long units = static_cast<long long>(x_tiles) * y_tiles * sp;
-          if (units > slots) break;
-          const bool better = units > best_units || (units == best_units && sp < skinny_splits);
-          if (better) {
-            best_units = units;
+          // 128-wide tiles run as light CTAs (two per SM) when there are more units than SMs
+          const long long slots = (bn_try <= 64 || units > sms) ? 2LL * sms : sms;
+          const long long rounds = (units + slots - 1) / slots;
+          if (rounds > 2) break;
+          const double kb_unit = static_cast<double>((kblocks + sp - 1) / sp);
+          const double in_round = static_cast<double>(units < slots ? units : slots);
+          const double hbm_us = (in_round / y_tiles) * 16384.0 * kb_unit / 5.5e6;  // the weight's bytes of one round
+          const double loop_us = kb_unit * 0.37 > hbm_us ? kb_unit * 0.37 : hbm_us;
+          const double us = rounds * loop_us + (rounds > 1 ? 3.0 : 0.0) + (sp > 1 ? 3.0 + 0.5 * sp * bn_try / 64.0 : 0.0) +
+                            0.7 * bn_try / 32.0;
+          if (us < best_us - 0.05) {
+            best_us = us;
             skinny_bn = bn_try;
             skinny_splits = sp;
           }
@@ -397,7 +410,7 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
   // no split-K
   const int want_pair = cfg ? cfg->cta_pair : 0;
   const bool no_split = !(cfg && cfg->splits > 1);
-  const bool pair_epi = pl.scale_mode == SCALE_EPILOGUE && (bn == 256 || (bn == 224 && ew == 4 && !general)) && no_split;
+  const bool pair_epi = pl.scale_mode == SCALE_EPILOGUE && (bn == 256 || ((bn == 224 || bn == 128) && ew == 4 && !general && !q2d)) && no_split;
   const bool pair_mx = pl.scale_mode == SCALE_MX && !general && (bn == 224 || !(cfg && cfg->bn > 0)) && no_split &&
                        !(pl.out_mode == OUT_QUANT_Y && q.qn > 32) && !(q2d && pl.qy > 32) && ew == 4;
   // promotion pairs: one scale group per 128-deep K block, eight promotion warps, no cross-lane quantisation
@@ -423,10 +436,11 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
   // M = 128: two rounds with one CTA per SM) run as light CTAs, two per SM.
   int two_per_sm = 0;
   if (!pl.pair && !general && pl.scale_mode == SCALE_EPILOGUE && bn == 128 && ew == 4 && pl.out_mode != OUT_QUANT_2D &&
-      pl.ry <= 128 && !(cfg && cfg->splits > 1)) {
+      pl.ry <= 128) {
     const long long t128 = static_cast<long long>((pl.rx + 127) / 128) * ((pl.ry + 127) / 128);
+    const int sp = cfg && cfg->splits > 0 ? cfg->splits : (skinny_splits > 0 ? skinny_splits : 1);
     const int env = light128_override();
-    if (env == 1 || (env < 0 && t128 > sms)) two_per_sm = 1;
+    if (env == 1 || (env < 0 && t128 * sp > sms)) two_per_sm = 1;
   }
   // promotion on CTA pairs: the lean loop where one Y scale covers a thread's whole column slice
   int single_y = 0;
@@ -513,7 +527,9 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
       if (sp > clusters / rem) sp = clusters / rem;
       if (sp > pl.kblocks / 8) sp = pl.kblocks / 8;
       const size_t unit_bytes = static_cast<size_t>(2) * bn * 128 * sizeof(float);
-      while (sp > 1 && static_cast<size_t>(rem) * sp * unit_bytes > (static_cast<size_t>(6) << 20)) --sp;
+      // (a problem with fewer tiles than pairs has nothing but sliced tiles: its workspace may grow further)
+      const size_t part_cap = static_cast<size_t>(rem == tiles ? 24 : 6) << 20;
+      while (sp > 1 && static_cast<size_t>(rem) * sp * unit_bytes > part_cap) --sp;
       if (sp > 1 && static_cast<size_t>(rem) * 16 * sizeof(unsigned int) + 256 <= 65536) {
         pl.tail_first = tiles - rem;
         pl.tail_splits = sp;
@@ -721,6 +737,8 @@ static int run_gemm(const mxb_problem_t& q, const mxb_config_t* cfg, const void*
   p.out_dtype = q.out_dtype;
   const int esz = is_fp8(q.out_dtype) ? 1 : 2;
   p.vec_ok = p.out_ys == 1 && (p.out_xs * esz) % 16 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+  if (!p.vec_ok && !quant && p.out_xs == 1 && (p.out_ys * esz) % 16 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0)
+    p.vec_ok = 2;  // 16-bit results stored along x: lanes trade values and store 16 bytes each
   p.oscale = out_scale;
   if (quant) {
     const bool cs_t = (q.flags & MXB_OUT_SCALE_TRANSPOSE) != 0;

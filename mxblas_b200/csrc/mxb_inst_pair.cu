@@ -28,6 +28,10 @@ static const KernelEntry kPair[] = {
     MXB_PAIR_ENTRY(128, SCALE_PROMOTE, OUT_HP, 8),       MXB_PAIR_ENTRY(128, SCALE_PROMOTE, OUT_QUANT_Y, 8),
     MXB_PAIR_ENTRY(224, SCALE_EPILOGUE, OUT_HP, 4),      MXB_PAIR_ENTRY(224, SCALE_EPILOGUE, OUT_QUANT_Y, 4),
     MXB_PAIR_ENTRY(224, SCALE_EPILOGUE, OUT_QUANT_X, 4),
+    // 256 x 128 tiles with scales constant along K: a decode-sized left operand (64 < M <= 128) as the Y operand,
+    // each CTA staging 128 rows of the weight and 64 rows of left per K block
+    MXB_PAIR_ENTRY(128, SCALE_EPILOGUE, OUT_HP, 4),      MXB_PAIR_ENTRY(128, SCALE_EPILOGUE, OUT_QUANT_Y, 4),
+    MXB_PAIR_ENTRY(128, SCALE_EPILOGUE, OUT_QUANT_X, 4),
 };
 const KernelEntry* pair_kernels(int* count) {
   *count = static_cast<int>(sizeof(kPair) / sizeof(kPair[0]));

@@ -47,7 +47,8 @@ struct GemmParams {
   void* out;
   long long out_xs, out_ys;  // element strides of out along x and y
   int out_dtype;             // DT_BF16 / DT_FP16 / DT_E4M3 / DT_E5M2
-  int vec_ok;                // out_ys == 1 and rows are 16-byte aligned: 16-byte vector stores allowed
+  int vec_ok;                // 16-byte vector stores allowed: 1 = along y (out_ys == 1, rows 16-byte aligned),
+                             // 2 = along x (16-bit results with out_xs == 1, y rows 16-byte aligned)
   void* oscale;
   long long os_xs, os_ys;    // QUANT_Y: index (x, y/qn); QUANT_X: index (x/qn, y); QUANT_2D: index (x/qx, y/qy)
   int qn;                    // quantisation group length
@@ -112,7 +113,7 @@ __device__ __forceinline__ float group_scale(float amax, float inv_fp8_max, int 
 // the kernels of the reference's own layout 4 % (same-box A/B on B200: 8192^3 per-tensor 364.5 -> 380 us).
 // SINGLE_Y_ (promotion only): every thread's column slice lies inside one scale block of Y, and the lean loop
 // promote_groups_single_y replaces the general one.
-template <int BN_, int SCALE_MODE_, int OUT_MODE_, int EPI_WARPS_, bool TWO_PER_SM_ = false, bool GENERAL_ = false,
+template <int BN_, int SCALE_MODE_, int OUT_MODE_, int EPI_WARPS_, int TWO_PER_SM_ = 0, bool GENERAL_ = false,
           bool SINGLE_Y_ = false>
 struct KernelCfg {
   static constexpr bool GENERAL = GENERAL_;
@@ -149,8 +150,8 @@ struct KernelCfg {
   // with four stages each: twice as many tiles stream concurrently, which takes the edge off wave
   // quantisation (224 tiles of config 5 no longer need two rounds on 148 SMs). Such a CTA takes
   // only the 128 TMEM columns it needs, so that two fit.
-  static constexpr bool LIGHT = (BN <= 64 || (BN == 128 && TWO_PER_SM_)) && SCALE_MODE == SCALE_EPILOGUE;
-  static_assert(!TWO_PER_SM_ || LIGHT, "two CTAs per SM: 128-wide tiles with scales applied in the epilogue");
+  static constexpr bool LIGHT = (BN <= 64 || (BN == 128 && TWO_PER_SM_ == 1)) && SCALE_MODE == SCALE_EPILOGUE;
+  static_assert(TWO_PER_SM_ == 0 || (TWO_PER_SM_ == 1 && LIGHT), "two CTAs per SM: 128-wide tiles with scales applied in the epilogue");
   static constexpr int CTAS_PER_SM = LIGHT ? 2 : 1;
   static constexpr int STAGES = LIGHT ? (BN == 128 ? 3 : 4) : ((STAGES_FIT > 8 ? 8 : STAGES_FIT) & ~1);
   // one full barrier per PAIR of stages (the MMA thread's wait costs it ~200 cycles), where the stage count is
@@ -238,10 +239,25 @@ struct OutputStage {
       // sum the split-K partial tiles in split order (deterministic); layout [split][BN][128]
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = 0.f;
-      for (int sp = 0; sp < p.splits; ++sp) {
+      // (16-bit results, the decode case: two slices' loads in flight at a time, one round trip to L2 per pair of
+      // slices; the quantising and the promotion kernels, short of registers, take one slice at a time)
+      constexpr int STEP = (Cfg::SCALE_MODE == SCALE_PROMOTE || Cfg::OUT_MODE != OUT_HP) ? 1 : 2;
+      for (int sp = 0; sp < p.splits; sp += STEP) {
         const float* w = acc + (static_cast<size_t>(sp) * Cfg::BN + c * 32) * 128;
+        const bool two = STEP == 2 && sp + 1 < p.splits;
+        float t0[32], t1[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] += __ldcg(w + j * 128);
+        for (int j = 0; j < 32; ++j) t0[j] = __ldcg(w + j * 128);
+        if (two) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) t1[j] = __ldcg(w + (Cfg::BN + j) * 128);
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] += t0[j];
+        if (two) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] += t1[j];
+        }
       }
       if (sy_s != nullptr) {
 #pragma unroll
@@ -262,12 +278,67 @@ struct OutputStage {
     }
   }
 
+  // Results stored along x (the lanes): a 32 x 32 block of the warp, lane = x, register = y, would go out as
+  // 32 two-byte stores per lane (64 contiguous bytes per warp and store; the load/store unit takes 16-bit
+  // stores a lane at a time: 10 us for a 128 x 128 tile, measured). Three butterfly steps over lane bits 0..2
+  // trade registers for neighbours' values, so that a lane ends up with eight consecutive x (16 bytes) of the
+  // four rows y = (lane & 7) + 8 i: four 16-byte stores per lane. All lanes of the warp must call this.
+  __device__ __forceinline__ void store_hp_along_x(int c, const float (&v)[32]) const {
+    const bool f16 = p.out_dtype == DT_FP16;
+    const bool b0 = (lane & 1) != 0, b1 = (lane & 2) != 0, b2 = (lane & 4) != 0;
+    uint32_t w1[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      // even lanes collect the even rows of the pair (x, x + 1), odd lanes the odd rows
+      const float recv = __shfl_xor_sync(0xffffffffu, b0 ? v[2 * i] : v[2 * i + 1], 1);
+      const float lo = b0 ? recv : v[2 * i], hi = b0 ? v[2 * i + 1] : recv;
+      w1[i] = f16 ? pack_f16x2(lo, hi) : pack_bf16x2(lo, hi);
+    }
+    uint32_t w2[8][2];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t recv = __shfl_xor_sync(0xffffffffu, b1 ? w1[2 * i] : w1[2 * i + 1], 2);
+      w2[i][0] = b1 ? recv : w1[2 * i];
+      w2[i][1] = b1 ? w1[2 * i + 1] : recv;
+    }
+    const int y0 = ycol0 + c * 32;
+    const int xg = xrow & ~7;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t r0 = __shfl_xor_sync(0xffffffffu, b2 ? w2[2 * i][0] : w2[2 * i + 1][0], 4);
+      const uint32_t r1 = __shfl_xor_sync(0xffffffffu, b2 ? w2[2 * i][1] : w2[2 * i + 1][1], 4);
+      uint4 w;
+      w.x = b2 ? r0 : w2[2 * i][0];
+      w.y = b2 ? r1 : w2[2 * i][1];
+      w.z = b2 ? w2[2 * i + 1][0] : r0;
+      w.w = b2 ? w2[2 * i + 1][1] : r1;
+      const int y = y0 + 8 * i + (lane & 7);
+      if (y < p.ry && xg < p.rx) {
+        uint16_t* dst = reinterpret_cast<uint16_t*>(p.out) + static_cast<long long>(y) * p.out_ys + xg;
+        if (xg + 8 <= p.rx) {
+          *reinterpret_cast<uint4*>(dst) = w;
+        } else {
+          const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+          for (int t = 0; t < 8; ++t)
+            if (xg + t < p.rx) dst[t] = static_cast<uint16_t>(ws[t >> 1] >> (16 * (t & 1)));
+        }
+      }
+    }
+  }
+
   // store 32 consecutive-y values of 16-bit type
   __device__ __forceinline__ void store_hp(int c, const float (&v)[32]) const {
+    if constexpr (!FROM_REGS) {  // (the promotion kernels, short of registers, keep their stores as they are)
+      if (p.vec_ok == 2) {       // uniform over the grid: no lane leaves before the shuffles
+        store_hp_along_x(c, v);
+        return;
+      }
+    }
     const int y0 = ycol0 + c * 32;
     if (xrow >= p.rx || y0 >= p.ry) return;
     const bool f16 = p.out_dtype == DT_FP16;
-    if (p.vec_ok && y0 + 32 <= p.ry) {
+    if (p.vec_ok == 1 && y0 + 32 <= p.ry) {
       uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.out) + xrow * p.out_xs + y0);
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
@@ -315,7 +386,7 @@ struct OutputStage {
                       : pack_fp8x4<false>(q[4 * i], q[4 * i + 1], q[4 * i + 2], q[4 * i + 3]);
     }
     uint8_t* base = reinterpret_cast<uint8_t*>(p.out) + xrow * p.out_xs;
-    if (p.vec_ok && y0 + 32 <= p.ry) {
+    if (p.vec_ok == 1 && y0 + 32 <= p.ry) {
       uint4* dst = reinterpret_cast<uint4*>(base + y0);
       dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
       dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
@@ -471,10 +542,18 @@ struct OutputStage {
   }
 
   __device__ __forceinline__ bool run_quant_x() const {
+    if constexpr (FROM_REGS) {
 #pragma unroll
-    for (int c = 0; c < Cfg::CHUNKS; ++c) {
-      const bool ok = p.qn >= 32 ? quant_x_chunk<32>(c) : quant_x_chunk<16>(c);
-      if (!ok) return false;
+      for (int c = 0; c < Cfg::CHUNKS; ++c) {
+        const bool ok = p.qn >= 32 ? quant_x_chunk<32>(c) : quant_x_chunk<16>(c);
+        if (!ok) return false;
+      }
+    } else {
+#pragma unroll 1
+      for (int c = 0; c < Cfg::CHUNKS; ++c) {  // a real loop (instruction cache, see run())
+        const bool ok = p.qn >= 32 ? quant_x_chunk<32>(c) : quant_x_chunk<16>(c);
+        if (!ok) return false;
+      }
     }
     return true;
   }
@@ -575,11 +654,22 @@ struct OutputStage {
     if constexpr (Cfg::OUT_MODE == OUT_QUANT_2D) {
       return run_quant_2d();
     } else if constexpr (Cfg::OUT_MODE == OUT_HP) {
+      if constexpr (FROM_REGS) {
 #pragma unroll
-      for (int c = 0; c < Cfg::CHUNKS; ++c) {
-        float v[32];
-        fetch(c, v);
-        store_hp(c, v);
+        for (int c = 0; c < Cfg::CHUNKS; ++c) {
+          float v[32];
+          fetch(c, v);
+          store_hp(c, v);
+        }
+      } else {
+        // a real loop: a CTA with a single tile runs this code once, straight from a cold instruction cache
+        // (unrolled four times, the output stage of a 128 x 128 tile took 8 us; measured)
+#pragma unroll 1
+        for (int c = 0; c < Cfg::CHUNKS; ++c) {
+          float v[32];
+          fetch(c, v);
+          store_hp(c, v);
+        }
       }
       return true;
     } else if constexpr (Cfg::OUT_MODE == OUT_QUANT_Y) {

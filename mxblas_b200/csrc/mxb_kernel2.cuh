@@ -88,7 +88,7 @@ struct PairCfg {
   }
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
   static_assert(STAGES % 2 == 0, "full barriers cover stage pairs");
-  static_assert(BN == 256 || (BN == 224 && SCALE_MODE != SCALE_PROMOTE) || (BN == 128 && SCALE_MODE == SCALE_PROMOTE),
+  static_assert(BN == 256 || (BN == 224 && SCALE_MODE != SCALE_PROMOTE) || (BN == 128 && SCALE_MODE != SCALE_MX),
                 "tile widths of the pair kernel");
   static_assert(NUM_ACC * ACC_STRIDE <= 512 && STAGES > NUM_ACC, "promotion: a stage's barrier is observed before it turns again");
   static_assert(SCALE_MODE != SCALE_MX || BN == 224, "block-scaled pairs use 224 columns");

@@ -94,6 +94,9 @@ def candidates(m: int, n: int, k: int, sk: int, quant: bool, out_transpose: bool
                         continue
                     for splits in (1, 2, 3, 4):
                         out.append(MxbConfig(bn, swap, 4, 8, splits, 0, 1))
+            if 64 < m <= 128:  # left as the 128-wide Y operand of a CTA pair, each CTA staging half of it
+                for tail in (0, 1):
+                    out.append(MxbConfig(128, 1, 4, 16, tail, 0, 2))
         else:
             for swap in swap_opts:
                 for ew in ((4, 8) if quant else (4,)):
