@@ -1111,8 +1111,14 @@ mx_gemm_sm100(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       // descriptor step from one 32-deep K slice to the next: 32 bytes along a K-major row, four 8-row groups
       // (4096 bytes) in an operand staged as K rows
       const uint32_t kstep_a = x_by_rows<Cfg>(p) ? 256u : 2u, kstep_b = y_by_rows<Cfg>(p) ? 256u : 2u;
-      const uint64_t ka[4] = {0, kstep_a, 2 * kstep_a, 3 * kstep_a}, kbs[4] = {0, kstep_b, 2 * kstep_b, 3 * kstep_b};
+      // the descriptors' high words are constants; their low words (address field, 16-byte units) step from stage
+      // to stage by one 32-bit addition
       const uint64_t hi_a = umma_desc_hi(x_by_rows<Cfg>(p)), hi_b = umma_desc_hi(y_by_rows<Cfg>(p));
+      const uint32_t a_hi = static_cast<uint32_t>(hi_a >> 32), b_hi = static_cast<uint32_t>(hi_b >> 32);
+      const uint32_t a_lo0 = static_cast<uint32_t>(hi_a) | ((smem_u32(sA) >> 4) & 0x3FFFu);
+      const uint32_t b_lo0 = static_cast<uint32_t>(hi_b) | ((smem_u32(sB) >> 4) & 0x3FFFu);
+      constexpr uint32_t A_STEP = Cfg::A_BYTES >> 4, B_STEP = Cfg::B_BYTES >> 4;
+      uint32_t a_lo = a_lo0, b_lo = b_lo0;  // of stage s
       // K elements accumulated in TMEM before the epilogue warps take the partial sum
       const int group_k = Cfg::SCALE_MODE == SCALE_PROMOTE ? p.gk : 0;
       for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
@@ -1146,9 +1152,6 @@ mx_gemm_sm100(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
               }
             }
           }
-          const uint32_t a_addr = smem_u32(sA + s * Cfg::A_BYTES);
-          const uint32_t b_addr = smem_u32(sB + s * Cfg::B_BYTES);
-          const uint64_t da0 = umma_desc_at(hi_a, a_addr), db0 = umma_desc_at(hi_b, b_addr);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             bool fresh = false;
@@ -1160,11 +1163,13 @@ mx_gemm_sm100(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
               open = true;
               fresh = true;
             }
-            const uint64_t da = da0 + ka[kk], db = db0 + kbs[kk];
+            const uint64_t da = umma_desc_words(a_lo + kk * kstep_a, a_hi), db = umma_desc_words(b_lo + kk * kstep_b, b_hi);
             if constexpr (Cfg::SCALE_MODE == SCALE_MX) {
               umma_mxf8(d_tmem, da, db, umma_idesc_sf_ids(idesc, kk, kk), fresh ? 0u : 1u,
                         tmem_base + Cfg::SFA_COL + (s & 1) * Cfg::SF_SLOT,
                         tmem_base + Cfg::SFB_COL + (s & 1) * Cfg::SF_SLOT);
+            } else if (Cfg::SCALE_MODE == SCALE_EPILOGUE && kk != 0) {
+              umma_f8_acc(d_tmem, da, db, idesc);  // an accumulator only opens on the first K slice of a K block
             } else {
               umma_f8(d_tmem, da, db, idesc, fresh ? 0u : 1u);
             }
@@ -1184,9 +1189,13 @@ mx_gemm_sm100(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
           }
           if (!ok) break;
           umma_commit(bar_empty + 8 * s);
+          a_lo += A_STEP;
+          b_lo += B_STEP;
           if (++s == STAGES) {
             s = 0;
             ph ^= 1;
+            a_lo = a_lo0;
+            b_lo = b_lo0;
           }
         }
       }

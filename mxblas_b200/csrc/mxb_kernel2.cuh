@@ -225,8 +225,19 @@ mx_gemm_sm100_pair(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                                                                           : umma_idesc_f8(256, BN, p.fmt_x, p.fmt_y),
                                               x_by_rows<Cfg>(p), y_by_rows<Cfg>(p));
       const uint32_t kstep_a = x_by_rows<Cfg>(p) ? 256u : 2u, kstep_b = y_by_rows<Cfg>(p) ? 256u : 2u;
-      const uint64_t ka[4] = {0, kstep_a, 2 * kstep_a, 3 * kstep_a}, kbs[4] = {0, kstep_b, 2 * kstep_b, 3 * kstep_b};
+      // This thread paces the pair's tensor cores (an artificial 100 cycles per K block in this loop cost config 2
+      // 12 % and config 4 10 %, measured), so per K block it does as little as it can: the descriptors' high
+      // words are constants, their low words (address field in 16-byte units) step from stage to stage by one
+      // 32-bit addition, the instruction descriptors of the four K slices are chosen here, and only the first
+      // MMA of a unit computes its accumulate predicate.
       const uint64_t hi_a = umma_desc_hi(x_by_rows<Cfg>(p)), hi_b = umma_desc_hi(y_by_rows<Cfg>(p));
+      const uint32_t a_hi = static_cast<uint32_t>(hi_a >> 32), b_hi = static_cast<uint32_t>(hi_b >> 32);
+      const uint32_t a_lo0 = static_cast<uint32_t>(hi_a) | ((smem_u32(sA) >> 4) & 0x3FFFu);
+      const uint32_t b_lo0 = static_cast<uint32_t>(hi_b) | ((smem_u32(sB) >> 4) & 0x3FFFu);
+      constexpr uint32_t A_STEP = Cfg::A_BYTES >> 4, B_STEP = Cfg::B_BYTES >> 4;
+      uint32_t a_lo = a_lo0, b_lo = b_lo0;  // of stage s
+      const uint32_t idesc_k[4] = {umma_idesc_sf_ids(idesc, 0, 0), umma_idesc_sf_ids(idesc, 1, 1),
+                                   umma_idesc_sf_ids(idesc, 2, 2), umma_idesc_sf_ids(idesc, 3, 3)};
       for (int u = pair; u < num_units && ok; u += num_pairs) {
         const PairUnit un = pair_unit(u, p);
         if (Cfg::GENERAL && p.x_group != nullptr && tile_group<Cfg>(p, tile_coord(un.t, p).tx * 256) < 0) continue;
@@ -249,32 +260,36 @@ mx_gemm_sm100_pair(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             tc_fence_after();
             d_tmem = tmem_base + b * Cfg::ACC_STRIDE;
           }
-          const uint64_t da0 = umma_desc_at(hi_a, smem_u32(sA + s * Cfg::A_BYTES));
-          const uint64_t db0 = umma_desc_at(hi_b, smem_u32(sB + s * Cfg::B_BYTES));
           if constexpr (Cfg::SCALE_MODE == SCALE_MX) {
             // the stage's scale factors are in TMEM slot `slot` of both CTAs (the full barrier counted
             // the scale-factor warps' arrivals)
-            const uint32_t sf = tmem_base + Cfg::sf_col(slot);
+            static_assert(Cfg::sf_col(2) == Cfg::sf_col(0) + 32 + 224 && Cfg::sf_col(3) == Cfg::sf_col(1) + 32 + 224, "slots");
+            const uint32_t sf = tmem_base + Cfg::sf_col(0) + 16u * slot + 112u * (slot & 2u);
+            umma_mxf8_pair(d_tmem, umma_desc_words(a_lo, a_hi), umma_desc_words(b_lo, b_hi), idesc_k[0],
+                           kb > un.kb0 ? 1u : 0u, sf, sf + Cfg::SFB_OFFSET);
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
-              umma_mxf8_pair(d_tmem, da0 + ka[kk], db0 + kbs[kk], umma_idesc_sf_ids(idesc, kk, kk),
-                             (kb > un.kb0 || kk != 0) ? 1u : 0u, sf, sf + Cfg::SFB_OFFSET);
+            for (int kk = 1; kk < 4; ++kk)
+              umma_mxf8_pair_acc(d_tmem, umma_desc_words(a_lo + kk * kstep_a, a_hi),
+                                 umma_desc_words(b_lo + kk * kstep_b, b_hi), idesc_k[kk], sf, sf + Cfg::SFB_OFFSET);
             slot = (slot + 1) & (Cfg::SF_SLOTS - 1);
-          } else if constexpr (Cfg::SCALE_MODE == SCALE_PROMOTE) {
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
-              umma_f8_pair(d_tmem, da0 + ka[kk], db0 + kbs[kk], idesc, kk != 0 ? 1u : 0u);
           } else {
+            const uint32_t first = (Cfg::SCALE_MODE == SCALE_PROMOTE || kb == un.kb0) ? 0u : 1u;
+            umma_f8_pair(d_tmem, umma_desc_words(a_lo, a_hi), umma_desc_words(b_lo, b_hi), idesc, first);
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
-              umma_f8_pair(d_tmem, da0 + ka[kk], db0 + kbs[kk], idesc, (kb > un.kb0 || kk != 0) ? 1u : 0u);
+            for (int kk = 1; kk < 4; ++kk)
+              umma_f8_pair_acc(d_tmem, umma_desc_words(a_lo + kk * kstep_a, a_hi),
+                               umma_desc_words(b_lo + kk * kstep_b, b_hi), idesc);
           }
           // the stage is free in both CTAs once these MMAs have read it (promotion: and the partial
           // sum of this K block is complete)
           umma_commit_pair_both(bar_empty + 8 * s, 3);
+          a_lo += A_STEP;
+          b_lo += B_STEP;
           if (++s == STAGES) {
             s = 0;
             ph ^= 1;
+            a_lo = a_lo0;
+            b_lo = b_lo0;
           }
           if constexpr (Cfg::SCALE_MODE == SCALE_PROMOTE) {
             if (++b == NUM_ACC) {

@@ -480,6 +480,19 @@ __device__ __forceinline__ void umma_f8_pair(uint32_t d_tmem, uint64_t a_desc, u
       : "memory");
 }
 
+// The same with the accumulate flag fixed at "add to D": no predicate to compute in the issuing thread.
+__device__ __forceinline__ void umma_f8_pair_acc(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.eq.u32 p, 1, 1;\n"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc)
+      : "memory");
+}
+
 // Same, but the arrival is delivered to the barrier at this shared-memory offset in every CTA of
 // `cta_mask` (bit i = CTA rank i of the cluster): one instruction releases a stage in both CTAs of a
 // pair. This multicasts a barrier SIGNAL only; no data load in this library is multicast.
@@ -503,6 +516,38 @@ __device__ __forceinline__ void umma_mxf8_pair(uint32_t d_tmem, uint64_t a_desc,
       :
       : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
       : "memory");
+}
+
+__device__ __forceinline__ void umma_mxf8_pair_acc(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                   uint32_t sfa_tmem, uint32_t sfb_tmem) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.eq.u32 p, 1, 1;\n"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%4], [%5], p;\n"
+      "}\n"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+
+// one-CTA forms with the accumulate flag fixed at "add to D"
+__device__ __forceinline__ void umma_f8_acc(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.eq.u32 p, 1, 1;\n"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc)
+      : "memory");
+}
+
+// A 64-bit shared-memory descriptor from its two words (the high word of an operand's descriptors never changes;
+// the low word holds the address field, which steps by plain 32-bit additions).
+__device__ __forceinline__ uint64_t umma_desc_words(uint32_t lo, uint32_t hi) {
+  return (static_cast<uint64_t>(hi) << 32) | lo;
 }
 
 }  // namespace mxb
