@@ -318,7 +318,8 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
   // measured on B200 with the timeline of a 128 x 8192 x 8192 call:
   //  * one MMA thread issues a 128-deep K block in ~0.37 us whatever the tile width, and two CTAs on one SM do
   //    not slow each other down: a unit's K loop costs 0.37 us per K block, so the work is cut into as many
-  //    units as there are slots (light CTAs: two per SM), unless the weight's bytes / 5.5 TB/s take longer;
+  //    units as there are slots (light CTAs: two per SM), unless the weight's bytes / 5.5 TB/s or all staged
+  //    bytes / 14 TB/s take longer;
   //  * a second round of units costs its K loop again plus ~3 us;
   //  * the split-K exchange costs ~3 us (park, fence, count) plus ~0.5 us per 32 KiB slice the last unit adds up;
   //  * the output stage costs ~0.7 us per 32 columns of the tile.
@@ -345,7 +346,12 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
           const double kb_unit = static_cast<double>((kblocks + sp - 1) / sp);
           const double in_round = static_cast<double>(units < slots ? units : slots);
           const double hbm_us = (in_round / y_tiles) * 16384.0 * kb_unit / 5.5e6;  // the weight's bytes of one round
-          const double loop_us = kb_unit * 0.37 > hbm_us ? kb_unit * 0.37 : hbm_us;
+          // everything the round's CTAs stage (HBM and L2 together fill shared memory at ~14 TB/s: 16 us per
+          // 128-deep K block of 256 units of 128 + 64 rows, measured)
+          const double fill_us = in_round * (128.0 + bn_try) * 128.0 * kb_unit / 14.0e6;
+          double loop_us = kb_unit * 0.37;
+          if (hbm_us > loop_us) loop_us = hbm_us;
+          if (fill_us > loop_us) loop_us = fill_us;
           const double us = rounds * loop_us + (rounds > 1 ? 3.0 : 0.0) + (sp > 1 ? 3.0 + 0.5 * sp * bn_try / 64.0 : 0.0) +
                             0.7 * bn_try / 32.0;
           if (us < best_us - 0.05) {
