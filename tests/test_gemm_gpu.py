@@ -579,6 +579,38 @@ def test_c_abi_direct_call_with_canaries():
     assert float((dist == 0).float().mean()) >= CODES_SAME and int(dist.max()) <= 1
 
 
+@pytest.mark.parametrize("m,n,ldc", [(48, 100, 104), (128, 332, 336), (16, 264, 264), (100, 4100, 4104)])
+def test_swapped_16_bit_results_in_a_padded_buffer(m, n, ldc):
+    """Skinny problems run with the operands swapped, so a warp's lanes run along N: the 16-byte stores along N
+    (lanes trade values first) must respect a ragged N (whole 8-column groups only), a row pitch wider than N and
+    the rows beyond M; bytes outside the result keep their canary."""
+    k = 512
+    left, right_phys, ls, rs = make_inputs(m, n, k, 1, 1, k, seed=77)
+    d = dev()
+    ld, rd, lsd, rsd = left.to(d), right_phys.to(d), ls.to(d), rs.to(d)
+    pad = 1024
+    canary = 0x7BCD
+    obuf = torch.full((m * ldc + 2 * pad,), canary, dtype=torch.int16, device=d)
+    problem = _direct_problem(m, n, k, 1, 1, k, False, 0)
+    problem.ldc = ldc
+    cfg = MxbConfig(0, 1, 0, 0, 0, 0)  # operands swapped
+    need = ctypes.c_size_t(0)
+    assert _ext.lib.mxb_query_workspace(ctypes.byref(problem), ctypes.byref(cfg), ctypes.byref(need)) == 0
+    ws = torch.zeros(max(need.value, 256), dtype=torch.uint8, device=d)
+    stream = torch.cuda.current_stream().cuda_stream
+    st = _ext.lib.mxb_gemm_cfg(ctypes.byref(problem), ctypes.byref(cfg), ld.data_ptr(), rd.data_ptr(),
+                               obuf.data_ptr() + 2 * pad, lsd.data_ptr(), rsd.data_ptr(), None, ws.data_ptr(),
+                               need.value, stream)
+    assert st == _ext.MXB_OK, _ext.status_text(st)
+    assert _ext.device_status() == 0
+    body = obuf[pad:pad + m * ldc].reshape(m, ldc)
+    assert bool((obuf[:pad] == canary).all()) and bool((obuf[pad + m * ldc:] == canary).all()), "write outside out"
+    assert bool((body[:, n:] == canary).all()), "write into the padding of a row"
+    got = body[:, :n].contiguous().view(torch.bfloat16).cpu().float()
+    met = orc.compare_hp(got, orc.mx_gemm_c32(left, right_phys.t(), ls, rs.t()))
+    assert met["max_rel"] <= HP_MAX_REL and met["cosine"] >= HP_COSINE, met
+
+
 def test_c_abi_workspace_protocol():
     m, n, k = 32, 1024, 4096
     left, right_phys, ls, rs = make_inputs(m, n, k, 1, 1, k, seed=61)
