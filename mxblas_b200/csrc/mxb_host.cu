@@ -745,6 +745,8 @@ static int run_gemm(const mxb_problem_t& q, const mxb_config_t* cfg, const void*
   p.vec_ok = p.out_ys == 1 && (p.out_xs * esz) % 16 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
   if (!p.vec_ok && !quant && p.out_xs == 1 && (p.out_ys * esz) % 16 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0)
     p.vec_ok = 2;  // 16-bit results stored along x: lanes trade values and store 16 bytes each
+  if (!p.vec_ok && quant && p.out_xs == 1 && p.out_ys % 16 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0)
+    p.vec_ok = 3;  // FP8 codes stored along x, the same way
   p.oscale = out_scale;
   if (quant) {
     const bool cs_t = (q.flags & MXB_OUT_SCALE_TRANSPOSE) != 0;

@@ -48,7 +48,8 @@ struct GemmParams {
   long long out_xs, out_ys;  // element strides of out along x and y
   int out_dtype;             // DT_BF16 / DT_FP16 / DT_E4M3 / DT_E5M2
   int vec_ok;                // 16-byte vector stores allowed: 1 = along y (out_ys == 1, rows 16-byte aligned),
-                             // 2 = along x (16-bit results with out_xs == 1, y rows 16-byte aligned)
+                             // 2 = along x (16-bit results with out_xs == 1, y rows 16-byte aligned),
+                             // 3 = along x (FP8 codes with out_xs == 1, y rows 16-byte aligned)
   void* oscale;
   long long os_xs, os_ys;    // QUANT_Y: index (x, y/qn); QUANT_X: index (x/qn, y); QUANT_2D: index (x/qx, y/qy)
   int qn;                    // quantisation group length
@@ -239,9 +240,11 @@ struct OutputStage {
       // sum the split-K partial tiles in split order (deterministic); layout [split][BN][128]
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = 0.f;
-      // (16-bit results, the decode case: two slices' loads in flight at a time, one round trip to L2 per pair of
-      // slices; the quantising and the promotion kernels, short of registers, take one slice at a time)
-      constexpr int STEP = (Cfg::SCALE_MODE == SCALE_PROMOTE || Cfg::OUT_MODE != OUT_HP) ? 1 : 2;
+      // (the decode cases, 16-bit results and narrow swapped tiles with quantised results: two slices' loads in
+      // flight at a time, one round trip to L2 per pair of slices; the other kernels, short of registers, take one
+      // slice at a time)
+      constexpr bool DECODE_OUT = Cfg::OUT_MODE == OUT_HP || (Cfg::OUT_MODE == OUT_QUANT_X && Cfg::BN <= 64);
+      constexpr int STEP = (Cfg::SCALE_MODE == SCALE_PROMOTE || !DECODE_OUT) ? 1 : 2;
       for (int sp = 0; sp < p.splits; sp += STEP) {
         const float* w = acc + (static_cast<size_t>(sp) * Cfg::BN + c * 32) * 128;
         const bool two = STEP == 2 && sp + 1 < p.splits;
@@ -375,9 +378,81 @@ struct OutputStage {
     }
   }
 
+  // FP8 codes stored along x (the lanes), the byte-sized sibling of store_hp_along_x: one-byte stores go through
+  // the load/store unit a lane at a time (32 of them per lane and chunk: ~2 us per chunk with four warps,
+  // measured). Four butterfly steps over lane bits 0..3, the first two on bytes (prmt), leave a lane with
+  // sixteen consecutive x of the two rows y = (lane & 15) + 16 t: two 16-byte stores per lane.
+  // w[i] holds the codes of y = 4 i .. 4 i + 3 of this lane's x. All lanes of the warp must call this.
+  __device__ __forceinline__ void store_fp8_along_x(int c, const uint32_t (&w)[8]) const {
+    const bool b0 = (lane & 1) != 0, b1 = (lane & 2) != 0, b2 = (lane & 4) != 0, b3 = (lane & 8) != 0;
+    uint32_t w1[8];  // w1[2 i + h]: x pair (l & ~1), rows 8 i + 4 h + b0 and that + 2
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t ev = __byte_perm(w[2 * i], w[2 * i + 1], 0x6420), od = __byte_perm(w[2 * i], w[2 * i + 1], 0x7531);
+      const uint32_t keep = b0 ? od : ev;
+      const uint32_t recv = __shfl_xor_sync(0xffffffffu, b0 ? ev : od, 1);
+      const uint32_t lo = b0 ? recv : keep, hi = b0 ? keep : recv;
+      w1[2 * i] = __byte_perm(lo, hi, 0x5140);
+      w1[2 * i + 1] = __byte_perm(lo, hi, 0x7362);
+    }
+    uint32_t w2[8];  // w2[2 i + h]: four x at (l & ~3), row 8 i + 4 h + 2 b1 + b0
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t lows = __byte_perm(w1[2 * i], w1[2 * i + 1], 0x5410), highs = __byte_perm(w1[2 * i], w1[2 * i + 1], 0x7632);
+      const uint32_t keep = b1 ? highs : lows;
+      const uint32_t recv = __shfl_xor_sync(0xffffffffu, b1 ? lows : highs, 2);
+      const uint32_t lo = b1 ? recv : keep, hi = b1 ? keep : recv;
+      w2[2 * i] = __byte_perm(lo, hi, 0x5410);
+      w2[2 * i + 1] = __byte_perm(lo, hi, 0x7632);
+    }
+    uint32_t d3[4][2];  // eight x at (l & ~7), row 8 i + (l & 7)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t keep = b2 ? w2[2 * i + 1] : w2[2 * i];
+      const uint32_t recv = __shfl_xor_sync(0xffffffffu, b2 ? w2[2 * i] : w2[2 * i + 1], 4);
+      d3[i][0] = b2 ? recv : keep;
+      d3[i][1] = b2 ? keep : recv;
+    }
+    const int y0 = ycol0 + c * 32;
+    const int xg = xrow & ~15;
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      const uint32_t k0 = b3 ? d3[2 * t + 1][0] : d3[2 * t][0], k1 = b3 ? d3[2 * t + 1][1] : d3[2 * t][1];
+      const uint32_t r0 = __shfl_xor_sync(0xffffffffu, b3 ? d3[2 * t][0] : d3[2 * t + 1][0], 8);
+      const uint32_t r1 = __shfl_xor_sync(0xffffffffu, b3 ? d3[2 * t][1] : d3[2 * t + 1][1], 8);
+      const uint4 v16 = b3 ? make_uint4(r0, r1, k0, k1) : make_uint4(k0, k1, r0, r1);
+      const int y = y0 + 16 * t + (lane & 15);
+      if (y < p.ry && xg < p.rx) {
+        uint8_t* dst = reinterpret_cast<uint8_t*>(p.out) + static_cast<long long>(y) * p.out_ys + xg;
+        if (xg + 16 <= p.rx) {
+          *reinterpret_cast<uint4*>(dst) = v16;
+        } else {
+          const uint32_t ws[4] = {v16.x, v16.y, v16.z, v16.w};
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (xg + i < p.rx) dst[i] = static_cast<uint8_t>(ws[i >> 2] >> (8 * (i & 3)));
+        }
+      }
+    }
+  }
+
   // store 32 consecutive-y fp8 codes; q[j] = v[j] * inv[j] already applied by the caller
   __device__ __forceinline__ void store_fp8(int c, const float (&q)[32]) const {
     const int y0 = ycol0 + c * 32;
+    // (only where quantisation groups run along x: a swapped, decode-sized problem; other kernels keep their
+    // register budget)
+    if constexpr (!FROM_REGS && Cfg::OUT_MODE == OUT_QUANT_X) {
+      if (p.vec_ok == 3) {  // uniform over the grid: no lane leaves before the shuffles
+        uint32_t wt[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          wt[i] = e5m2_out ? pack_fp8x4<true>(q[4 * i], q[4 * i + 1], q[4 * i + 2], q[4 * i + 3])
+                           : pack_fp8x4<false>(q[4 * i], q[4 * i + 1], q[4 * i + 2], q[4 * i + 3]);
+        }
+        store_fp8_along_x(c, wt);
+        return;
+      }
+    }
     if (xrow >= p.rx || y0 >= p.ry) return;
     uint32_t w[8];
 #pragma unroll

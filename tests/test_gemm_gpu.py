@@ -611,6 +611,39 @@ def test_swapped_16_bit_results_in_a_padded_buffer(m, n, ldc):
     assert met["max_rel"] <= HP_MAX_REL and met["cosine"] >= HP_COSINE, met
 
 
+@pytest.mark.parametrize("m,n,ldc,qn", [(48, 112, 128, 16), (128, 352, 352, 32), (16, 4112, 4128, 16), (100, 1040, 1040, 16)])
+def test_swapped_fp8_results_in_a_padded_buffer(m, n, ldc, qn):
+    """The same for quantised results: FP8 codes of a swapped problem go out as 16-byte stores along N."""
+    k = 512
+    left, right_phys, ls, rs = make_inputs(m, n, k, 1, 1, k, seed=78)
+    d = dev()
+    ld, rd, lsd, rsd = left.to(d), right_phys.to(d), ls.to(d), rs.to(d)
+    pad = 1024
+    obuf = torch.full((m * ldc + 2 * pad,), 0xAB, dtype=torch.uint8, device=d)
+    sbuf = torch.full((m * (n // qn),), -7.0, dtype=torch.float32, device=d)
+    problem = _direct_problem(m, n, k, 1, 1, k, True, qn)
+    problem.ldc = ldc
+    cfg = MxbConfig(0, 1, 0, 0, 0, 0)  # operands swapped
+    need = ctypes.c_size_t(0)
+    assert _ext.lib.mxb_query_workspace(ctypes.byref(problem), ctypes.byref(cfg), ctypes.byref(need)) == 0
+    ws = torch.zeros(max(need.value, 256), dtype=torch.uint8, device=d)
+    stream = torch.cuda.current_stream().cuda_stream
+    st = _ext.lib.mxb_gemm_cfg(ctypes.byref(problem), ctypes.byref(cfg), ld.data_ptr(), rd.data_ptr(),
+                               obuf.data_ptr() + pad, lsd.data_ptr(), rsd.data_ptr(), sbuf.data_ptr(), ws.data_ptr(),
+                               need.value, stream)
+    assert st == _ext.MXB_OK, _ext.status_text(st)
+    assert _ext.device_status() == 0
+    body = obuf[pad:pad + m * ldc].reshape(m, ldc)
+    assert bool((obuf[:pad] == 0xAB).all()) and bool((obuf[pad + m * ldc:] == 0xAB).all()), "write outside out"
+    assert bool((body[:, n:] == 0xAB).all()), "write into the padding of a row"
+    c32 = orc.mx_gemm_c32(left, right_phys.t(), ls, rs.t())
+    codes, scales, _ = orc.quantize_groups(c32, qn, torch.float32)
+    got = body[:, :n].contiguous().view(torch.float8_e4m3fn).cpu()
+    dist = orc.fp8_code_distance(got, codes)
+    assert float((dist == 0).float().mean()) >= CODES_SAME and int(dist.max()) <= 1
+    assert ((sbuf.reshape(m, n // qn).cpu() - scales.float()).abs() / scales.float()).max().item() <= SCALE_REL
+
+
 def test_c_abi_workspace_protocol():
     m, n, k = 32, 1024, 4096
     left, right_phys, ls, rs = make_inputs(m, n, k, 1, 1, k, seed=61)
