@@ -247,34 +247,23 @@ mx_gemm_sm100_pair(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
           tc_fence_after();
         }
         uint32_t d_tmem = tmem_base + b * Cfg::ACC_STRIDE;
-        for (int kb = un.kb0; kb < un.kb1; ++kb) {
-          if ((s & 1) == 0) {  // both stages of the pair have landed once this barrier completes
-            ok = mbar_wait_cluster(bar_full + 8 * s, ph, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL);
-            if (!ok) break;
-            tc_fence_after();
-          }
-          if constexpr (Cfg::SCALE_MODE == SCALE_PROMOTE) {
-            // one partial sum per K block, alternating between the two TMEM buffers
-            ok = mbar_wait_cluster(bar_tempty + 8 * b, aph ^ 1, abort_flag, p.status, DEV_TIMEOUT_MMA_TMEM);
-            if (!ok) break;
-            tc_fence_after();
-            d_tmem = tmem_base + b * Cfg::ACC_STRIDE;
-          }
+        // the four MMAs of the K block staged in `s`, the commit that hands the stage back, and the step to the
+        // next stage (without the wrap, which only follows an odd stage)
+        auto issue_stage = [&](uint32_t accumulate) {
           if constexpr (Cfg::SCALE_MODE == SCALE_MX) {
             // the stage's scale factors are in TMEM slot `slot` of both CTAs (the full barrier counted
             // the scale-factor warps' arrivals)
             static_assert(Cfg::sf_col(2) == Cfg::sf_col(0) + 32 + 224 && Cfg::sf_col(3) == Cfg::sf_col(1) + 32 + 224, "slots");
             const uint32_t sf = tmem_base + Cfg::sf_col(0) + 16u * slot + 112u * (slot & 2u);
-            umma_mxf8_pair(d_tmem, umma_desc_words(a_lo, a_hi), umma_desc_words(b_lo, b_hi), idesc_k[0],
-                           kb > un.kb0 ? 1u : 0u, sf, sf + Cfg::SFB_OFFSET);
+            umma_mxf8_pair(d_tmem, umma_desc_words(a_lo, a_hi), umma_desc_words(b_lo, b_hi), idesc_k[0], accumulate, sf,
+                           sf + Cfg::SFB_OFFSET);
 #pragma unroll
             for (int kk = 1; kk < 4; ++kk)
               umma_mxf8_pair_acc(d_tmem, umma_desc_words(a_lo + kk * kstep_a, a_hi),
                                  umma_desc_words(b_lo + kk * kstep_b, b_hi), idesc_k[kk], sf, sf + Cfg::SFB_OFFSET);
             slot = (slot + 1) & (Cfg::SF_SLOTS - 1);
           } else {
-            const uint32_t first = (Cfg::SCALE_MODE == SCALE_PROMOTE || kb == un.kb0) ? 0u : 1u;
-            umma_f8_pair(d_tmem, umma_desc_words(a_lo, a_hi), umma_desc_words(b_lo, b_hi), idesc, first);
+            umma_f8_pair(d_tmem, umma_desc_words(a_lo, a_hi), umma_desc_words(b_lo, b_hi), idesc, accumulate);
 #pragma unroll
             for (int kk = 1; kk < 4; ++kk)
               umma_f8_pair_acc(d_tmem, umma_desc_words(a_lo + kk * kstep_a, a_hi),
@@ -285,16 +274,61 @@ mx_gemm_sm100_pair(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
           umma_commit_pair_both(bar_empty + 8 * s, 3);
           a_lo += A_STEP;
           b_lo += B_STEP;
-          if (++s == STAGES) {
+          ++s;
+        };
+        auto wrap_ring = [&]() {
+          if (s == static_cast<uint32_t>(STAGES)) {
             s = 0;
             ph ^= 1;
             a_lo = a_lo0;
             b_lo = b_lo0;
           }
-          if constexpr (Cfg::SCALE_MODE == SCALE_PROMOTE) {
+        };
+        if constexpr (Cfg::SCALE_MODE == SCALE_PROMOTE) {
+          for (int kb = un.kb0; kb < un.kb1; ++kb) {
+            if ((s & 1) == 0) {  // both stages of the pair have landed once this barrier completes
+              ok = mbar_wait_cluster(bar_full + 8 * s, ph, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL);
+              if (!ok) break;
+              tc_fence_after();
+            }
+            // one partial sum per K block, alternating between the TMEM buffers
+            ok = mbar_wait_cluster(bar_tempty + 8 * b, aph ^ 1, abort_flag, p.status, DEV_TIMEOUT_MMA_TMEM);
+            if (!ok) break;
+            tc_fence_after();
+            d_tmem = tmem_base + b * Cfg::ACC_STRIDE;
+            issue_stage(0u);
+            wrap_ring();
             if (++b == NUM_ACC) {
               b = 0;
               aph ^= 1;
+            }
+          }
+        } else {
+          // Whole stage pairs per turn (one full barrier covers a pair): one wait, eight MMAs, two commits, one
+          // wrap test. A unit may begin on the second stage of a pair (the previous unit passed its barrier) and
+          // end on the first (the pair's barrier then also covers the next unit's first K block).
+          int kb = un.kb0;
+          uint32_t accumulate = 0;
+          if ((s & 1) != 0 && kb < un.kb1) {
+            issue_stage(accumulate);
+            accumulate = 1;
+            wrap_ring();
+            ++kb;
+          }
+          for (; kb + 2 <= un.kb1; kb += 2) {
+            ok = mbar_wait_cluster(bar_full + 8 * s, ph, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL);
+            if (!ok) break;
+            tc_fence_after();
+            issue_stage(accumulate);
+            accumulate = 1;
+            issue_stage(1u);
+            wrap_ring();
+          }
+          if (ok && kb < un.kb1) {
+            ok = mbar_wait_cluster(bar_full + 8 * s, ph, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL);
+            if (ok) {
+              tc_fence_after();
+              issue_stage(accumulate);
             }
           }
         }
