@@ -316,12 +316,13 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
   // Skinny problems whose 128-row tiles alone cannot occupy the GPU (a decode step against a weight of a few
   // thousand rows): the tile width along Y and the K split are chosen by a cost estimate. What it knows, all
   // measured on B200 with the timeline of a 128 x 8192 x 8192 call:
-  //  * one MMA thread issues a 128-deep K block in ~0.37 us whatever the tile width, and two CTAs on one SM do
-  //    not slow each other down: a unit's K loop costs 0.37 us per K block, so the work is cut into as many
-  //    units as there are slots (light CTAs: two per SM), unless the weight's bytes / 5.5 TB/s or all staged
-  //    bytes / 14 TB/s take longer;
+  //  * one MMA thread gets through a 128-deep K block in 0.25-0.31 us whatever the tile width, and two CTAs on
+  //    one SM do not slow each other down: a unit's K loop costs that much per K block, so the work is cut into
+  //    as many units as there are slots (light CTAs: two per SM), unless the weight's bytes / 5.5 TB/s or all
+  //    staged bytes / 14 TB/s take longer;
   //  * a second round of units costs its K loop again plus ~3 us;
-  //  * the split-K exchange costs ~3 us (park, fence, count) plus ~0.5 us per 32 KiB slice the last unit adds up;
+  //  * the split-K exchange costs ~0.5 us plus ~1.1 us per slice (park, fence, count, the last unit's round
+  //    trips to L2), a little more for 128-wide tiles;
   //  * the output stage costs ~0.7 us per 32 columns of the tile.
   // Measured over M = 16..128, N = 4096..10240, K = 7168..28672: within 10 % of the best of all candidates.
   int skinny_bn = 0, skinny_splits = 0;
@@ -349,11 +350,13 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
           // everything the round's CTAs stage (HBM and L2 together fill shared memory at ~14 TB/s: 16 us per
           // 128-deep K block of 256 units of 128 + 64 rows, measured)
           const double fill_us = in_round * (128.0 + bn_try) * 128.0 * kb_unit / 14.0e6;
-          double loop_us = kb_unit * 0.37;
+          // the MMA thread's pace: 0.25 us per K block with six stages (a 128-wide tile alone on its SM), 0.31 us
+          // as a light CTA with three or four
+          double loop_us = kb_unit * ((bn_try == 128 && units <= sms) ? 0.25 : 0.31);
           if (hbm_us > loop_us) loop_us = hbm_us;
           if (fill_us > loop_us) loop_us = fill_us;
-          const double us = rounds * loop_us + (rounds > 1 ? 3.0 : 0.0) + (sp > 1 ? 3.0 + 0.5 * sp * bn_try / 64.0 : 0.0) +
-                            0.7 * bn_try / 32.0;
+          const double exchange_us = sp > 1 ? 0.5 + 1.1 * sp + (bn_try == 128 ? 0.3 * sp : 0.0) : 0.0;
+          const double us = rounds * loop_us + (rounds > 1 ? 3.0 : 0.0) + exchange_us + 0.7 * bn_try / 32.0;
           if (us < best_us - 0.05) {
             best_us = us;
             skinny_bn = bn_try;
@@ -368,6 +371,26 @@ static int choose_plan(const mxb_problem_t& q, const mxb_config_t* cfg, Plan& pl
   int bn = cfg && cfg->bn > 0 ? cfg->bn : skinny_bn;
   if (bn == 0) {
     bn = pick_bn(pl.ry);
+    if (pl.scale_mode == SCALE_EPILOGUE && bn == 256 && !general && !q2d && !grp && !(cfg && cfg->splits > 1)) {
+      // Width of wide tiles with scales constant along K, both rules measured on B200 with K = 8192:
+      //  * where CTA pairs take the problem (same test as below), 256 x 224 tiles if that leaves fewer rounds x
+      //    width to run: M = 1024, N = 28672 152.6 against 167.9 us, M = 4096, N = 7168 147.5 against 161.8 us,
+      //    M = 1024, N = 3584 32.8 against 36.9 us; 8192^3 ties (14 x 256 = 16 x 224) and stays on 256;
+      //  * where they do not and the 128 x 128 tiles fit one round, those instead of half as many 128 x 256 tiles
+      //    cut along K: M = 256, N = 7168 26.6 against 33.8 us, M = 256, N = 3584 22.5 against 33.8 us.
+      const long long pairs = sms / 2 > 0 ? sms / 2 : 1;
+      const long long xt = (pl.rx + 255) / 256;
+      const long long pt256 = xt * ((pl.ry + 255) / 256), pt224 = xt * ((pl.ry + 223) / 224);
+      const bool pairs_run = pl.rx >= 256 && pt256 >= sms / 2 && !(cfg && cfg->cta_pair == 1);
+      if (pairs_run) {
+        const long long cost256 = ((pt256 + pairs - 1) / pairs) * 256, cost224 = ((pt224 + pairs - 1) / pairs) * 224;
+        const bool groups_fit = pl.out_mode != OUT_QUANT_Y || 224 % q.qn == 0;
+        if (groups_fit && cost224 * 100 < cost256 * 97) bn = 224;
+      } else {
+        const long long t128 = static_cast<long long>((pl.rx + 127) / 128) * ((pl.ry + 127) / 128);
+        if (t128 <= sms) bn = 128;
+      }
+    }
     if (pl.scale_mode == SCALE_PROMOTE && bn > 128) {
       // 128 x 256 tiles halve the shared-memory traffic per flop, which bounds the 128 x 128 kernel;
       // they need enough tiles to fill the GPU and have no cross-lane quantisation variant

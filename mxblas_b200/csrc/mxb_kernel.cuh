@@ -1201,6 +1201,88 @@ mx_gemm_sm100(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         if (Cfg::GENERAL && p.x_group != nullptr && tile_group<Cfg>(p, tile_coord(t, p).tx * 128) < 0) continue;
         const int kb0 = kb_lo(sp), kb1 = kb_lo(sp + 1);
         uint32_t d_tmem = 0;
+        if constexpr (Cfg::SCALE_MODE != SCALE_PROMOTE && Cfg::PAIRED_FULL) {
+          // One accumulator per unit and one full barrier per stage pair: whole pairs per turn (one wait, eight
+          // MMAs, two commits, one wrap test), like the CTA-pair kernel. A unit may begin on the second stage of
+          // a pair (the previous unit passed its barrier) and end on the first.
+          ok = mbar_wait(bar_tempty + 8 * b, aph ^ 1, abort_flag, p.status, DEV_TIMEOUT_MMA_TMEM);
+          if (!ok) break;
+          tc_fence_after();
+          d_tmem = tmem_base + b * Cfg::ACC_STRIDE;
+          auto copy_scale_factors = [&]() {  // block-scaled: the factors of both stages of the pair that starts at s
+            if constexpr (Cfg::SCALE_MODE == SCALE_MX) {
+#pragma unroll
+              for (uint32_t j = 0; j < 2; ++j) {
+                const uint32_t sj = s + j;
+                tmem_cp_32x128b_warpx4(tmem_base + Cfg::SFA_COL + j * Cfg::SF_SLOT,
+                                       umma_desc_rows16(smem_u32(sSFA + sj * Cfg::SFA_BYTES)));
+#pragma unroll
+                for (int a = 0; a < Cfg::Y_ATOMS; ++a)
+                  tmem_cp_32x128b_warpx4(tmem_base + Cfg::SFB_COL + j * Cfg::SF_SLOT + 4 * a,
+                                         umma_desc_rows16(smem_u32(sSFB + sj * Cfg::SFB_BYTES + a * 512)));
+              }
+            }
+          };
+          auto issue_stage = [&](uint32_t accumulate) {
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              const uint64_t da = umma_desc_words(a_lo + kk * kstep_a, a_hi), db = umma_desc_words(b_lo + kk * kstep_b, b_hi);
+              if constexpr (Cfg::SCALE_MODE == SCALE_MX) {
+                umma_mxf8(d_tmem, da, db, umma_idesc_sf_ids(idesc, kk, kk), kk == 0 ? accumulate : 1u,
+                          tmem_base + Cfg::SFA_COL + (s & 1) * Cfg::SF_SLOT, tmem_base + Cfg::SFB_COL + (s & 1) * Cfg::SF_SLOT);
+              } else if (kk == 0) {
+                umma_f8(d_tmem, da, db, idesc, accumulate);
+              } else {
+                umma_f8_acc(d_tmem, da, db, idesc);
+              }
+            }
+            umma_commit(bar_empty + 8 * s);
+            a_lo += A_STEP;
+            b_lo += B_STEP;
+            ++s;
+          };
+          auto wrap_ring = [&]() {
+            if (s == static_cast<uint32_t>(STAGES)) {
+              s = 0;
+              ph ^= 1;
+              a_lo = a_lo0;
+              b_lo = b_lo0;
+            }
+          };
+          int kb = kb0;
+          uint32_t accumulate = 0;
+          if ((s & 1) != 0 && kb < kb1) {
+            issue_stage(accumulate);
+            accumulate = 1;
+            wrap_ring();
+            ++kb;
+          }
+          for (; kb + 2 <= kb1; kb += 2) {
+            ok = mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL);
+            if (!ok) break;
+            tc_fence_after();
+            copy_scale_factors();
+            issue_stage(accumulate);
+            accumulate = 1;
+            issue_stage(1u);
+            wrap_ring();
+          }
+          if (ok && kb < kb1) {
+            ok = mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, DEV_TIMEOUT_MMA_FULL);
+            if (ok) {
+              tc_fence_after();
+              copy_scale_factors();
+              issue_stage(accumulate);
+            }
+          }
+          if (!ok) break;
+          umma_commit(bar_tfull + 8 * b);
+          if (++b == NUM_ACC) {
+            b = 0;
+            aph ^= 1;
+          }
+          continue;
+        }
         int gpos = 0;       // K elements already in the open scale group (split ranges start on a group)
         bool open = false;  // an accumulator buffer is currently being filled
         for (int kb = kb0; kb < kb1 && ok; ++kb) {

@@ -244,13 +244,18 @@ def autotune(left, right, left_scale, right_scale, output_quant=False, quant_siz
     cands = list(configs) if configs is not None else candidates(meta.m, meta.n, meta.k, meta.sk, meta.quant,
                                                                  meta.out_transpose, mx)
     results = []
-    for cfg in cands:
-        def run(cfg=cfg):
+
+    def timed(cfg):
+        def run():
             return mx_gemm_kernel(left, right, left_scale, right_scale, output_quant, quant_size, out_dtype,
                                   out_transpose, out_scale_transpose, out_scale_pow2=out_scale_pow2,
                                   pow2_scales=pow2_scales, config=cfg)
+        med, _ = time_call(run, iters=iters, warmup=2)
+        return med
+
+    for cfg in cands:
         try:
-            med, _ = time_call(run, iters=iters, warmup=2)
+            med = timed(cfg)
         except ValueError:
             continue  # the library has no kernel for this candidate
         if _ext.device_status() != 0:
@@ -263,6 +268,18 @@ def autotune(left, right, left_scale, right_scale, output_quant=False, quant_siz
                 f.write(f"{table_key(meta, out_scale_pow2, pow2_scales)} {cfg.key()} {med * 1e6:.2f}\n")
     if not results:
         raise ValueError("autotune: no candidate configuration ran")
+    # The first candidate (the heuristic plan) is timed right after the caller produced its operands, with the GPU
+    # in whatever clock state that left (measured: 43 us against 20.6 us for the same plan a moment later), so it
+    # and the provisional winner are timed once more, back to back, and each keeps its better figure.
+    by_key = dict(results)
+    first_key = results[0][0]
+    provisional = min(results, key=lambda r: r[1])[0]
+    for key in dict.fromkeys((first_key, provisional)):
+        try:
+            by_key[key] = min(by_key[key], timed(MxbConfig(*key)))
+        except ValueError:
+            pass
+    results = [(k, by_key[k]) for k, _ in results]
     best_key, best_t = min(results, key=lambda r: r[1])
     if persist:
         with _lock:

@@ -148,12 +148,18 @@ def _problem(m, n, k, sm, sn, sk, quant=False, qn=16, sdt=torch.float32, **kw):
 def test_plan_selection_without_a_gpu():
     """mxb_default_config / mxb_query_workspace are pure host code."""
     cases = {
-        "c1": (_problem(256, 256, 256, 256, 256, 256), dict(bn=256, swap=0, splits=1), False),
+        "c1": (_problem(256, 256, 256, 256, 256, 256), dict(bn=128, swap=0, splits=1), False),
         "c2": (_problem(8192, 8192, 8192, 8192, 8192, 8192, True, 16, torch.bfloat16), dict(bn=256, swap=0), False),
         "c3": (_problem(4096, 7168, 7168, 1, 128, 128, pow2=False), dict(swap=0, splits=1), True),  # K-sliced tail tiles
         "c4": (_problem(16384, 8192, 8192, 1, 1, 32, True, 32, out_t=True, pow2=True), dict(swap=1), True),
         "c5_16": (_problem(16, 28672, 8192, 1, 1, 8192), dict(bn=32, swap=1), None),
         "c5_16384": (_problem(16384, 28672, 8192, 1, 1, 8192), dict(bn=256, swap=0, splits=1), False),
+        # seven rounds of 256 x 224 CTA-pair tiles instead of seven of 256 x 256
+        "c5_1024": (_problem(1024, 28672, 8192, 1, 1, 8192), dict(bn=224, swap=0, cta_pair=2), None),
+        # too few tiles for CTA pairs: 112 tiles of 128 x 128 in one round, K not cut
+        "c5_256_shard": (_problem(256, 7168, 8192, 1, 1, 8192), dict(bn=128, swap=0, splits=1, cta_pair=1), False),
+        # a decode step against a mid-sized weight: 128-wide tiles, K cut in two (cost estimate)
+        "decode_128": (_problem(128, 8192, 8192, 128, 8192, 8192), dict(bn=128, swap=1, splits=2), True),
     }
     for name, (p, want, needs_ws) in cases.items():
         cfg = _ext.MxbConfig()
