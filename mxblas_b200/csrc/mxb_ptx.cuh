@@ -204,14 +204,11 @@ __device__ __forceinline__ uint64_t umma_desc_mn128(uint32_t addr, uint32_t bloc
   d |= static_cast<uint64_t>(2) << 61;
   return d;
 }
-// The MMA-issuing thread is a serial resource (every instruction between two MMAs is exposed), so per stage it
-// only ORs the stage's address into a descriptor whose constant bits were chosen once, outside the loops:
-// umma_desc_hi gives those bits for either operand form, umma_desc_at adds the address.
+// The MMA-issuing thread is a serial resource (every instruction between two MMAs is exposed), so the constant
+// bits of a descriptor are chosen once, outside the loops (umma_desc_hi, for either operand form), and per stage
+// only the address field of the low word steps (umma_desc_words).
 __device__ __forceinline__ uint64_t umma_desc_hi(int mn_major) {
   return mn_major ? (umma_desc_mn128(0, 16384)) : (umma_desc_k128(0));
-}
-__device__ __forceinline__ uint64_t umma_desc_at(uint64_t hi, uint32_t addr) {
-  return hi | static_cast<uint64_t>((addr >> 4) & 0x3FFF);
 }
 
 // instruction-descriptor bits for operands that are M-/N-major (bit 15: A, bit 16: B); valid for the 8-bit types
@@ -303,17 +300,8 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
-// registers -> TMEM: lane i of the warp writes 16 consecutive 32-bit columns of TMEM lane (base lane + i);
+// registers -> TMEM: lane i of the warp writes 32 consecutive 32-bit columns of TMEM lane (base lane + i);
 // same lane-quadrant rule as the loads
-__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-      : "memory");
-}
-// the same for 32 consecutive columns
 __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
