@@ -556,6 +556,27 @@ def _direct_problem(m, n, k, sm, sn, sk, quant, qn, out_t=False, scale_dtype=tor
     return make_problem(meta, m if out_t else n, n // qn if quant else 0, False, False)
 
 
+@pytest.mark.parametrize("m,n,k,sm,sn,sk,quant,config", [
+    # one-CTA kernels, two light CTAs per SM: 400 tiles on 296 slots, five K blocks each, so a CTA's second tile
+    # starts on the second stage of a pair and ends on the first
+    (16, 51200, 640, 16, 51200, 640, False, None),
+    (16, 51200, 640, 1, 1, 640, True, None),
+    # CTA pairs: 200 tiles on 74 pairs, seven K blocks each on a ring of six stages
+    (512, 25600, 896, 512, 25600, 896, True, MxbConfig(256, 0, 8, 8, 1, 0, 2)),
+    (512, 25600, 896, 1, 1, 896, False, MxbConfig(224, 0, 4, 16, 1, 0, 2)),
+    # block-scaled CTA pairs, seven K blocks
+    (512, 25536, 896, 1, 1, 32, False, None),
+    # one CTA per 128 x 256 tile, 400 tiles on 148 SMs, three K blocks (fewer than the stages)
+    (256, 51200, 384, 1, 1, 384, False, MxbConfig(256, 0, 4, 8, 1, 0, 1)),
+])
+def test_many_tiles_per_cta_with_odd_k_block_counts(m, n, k, sm, sn, sk, quant, config):
+    """The MMA threads take whole stage pairs per turn; a unit may begin on the second stage of a pair and end on
+    the first. Persistent CTAs with an odd number of K blocks per tile go through every such case."""
+    mx = sk == 32
+    left, right_phys, ls, rs = make_inputs(m, n, k, sm, sn, sk, seed=91, pow2=mx) if mx else make_inputs(m, n, k, sm, sn, sk, seed=91)
+    run_case(left, right_phys, ls, rs, quant=quant, qn=16, config=config, pow2_scales=mx)
+
+
 def test_c_abi_direct_call_with_canaries():
     m, n, k, qn = 200, 336, 272, 16
     left, right_phys, ls, rs = make_inputs(m, n, k, 1, 1, k, seed=60)
