@@ -228,3 +228,25 @@ def test_c_abi_layout_flags_and_grouped_plans():
     assert _ext.lib.mxb_grouped_query_workspace(ctypes.byref(plain), ctypes.byref(pair), 4, 128, ctypes.byref(nbytes)) == \
         _ext.MXB_ERR_UNSUPPORTED  # CTA pairs need blocks of whole 256-row tiles
     assert _ext.lib.mxb_grouped_query_workspace(ctypes.byref(plain), ctypes.byref(pair), 2, 256, ctypes.byref(nbytes)) == _ext.MXB_OK
+
+
+def test_every_plan_of_a_problem_grid_has_a_kernel():
+    """Planner sweep without a GPU: every valid problem of a grid over M, N, K, the four scaling patterns, the
+    quantisation group lengths and both output orientations gets a plan for which a kernel exists (the width
+    rules, the skinny cost estimate and the CTA-pair decisions never pick a combination that was not built)."""
+    import itertools
+
+    checked = 0
+    for m, n, k in itertools.product((1, 16, 48, 64, 100, 128, 200, 256, 512, 1024, 4096, 16384),
+                                     (128, 256, 1024, 3584, 7168, 8192, 28672), (128, 512, 8192)):
+        patterns = {"TT": (m, n, k), "CC": (1, 1, k), "GB": (1, 128, 128), "MX": (1, 1, 32)}
+        for name, (sm, sn, sk) in patterns.items():
+            for qn, out_t in itertools.product((0, 16, 32, 64, 128), (False, True)):
+                p = _problem(m, n, k, sm, sn, sk, bool(qn), qn or 16, out_t=out_t, pow2=True if name == "MX" else None)
+                cfg, nbytes = _ext.MxbConfig(), ctypes.c_size_t(0)
+                assert _ext.lib.mxb_default_config(ctypes.byref(p), ctypes.byref(cfg)) == _ext.MXB_OK, (m, n, k, name, qn, out_t)
+                assert _ext.lib.mxb_query_workspace(ctypes.byref(p), None, ctypes.byref(nbytes)) == _ext.MXB_OK
+                assert cfg.bn in (32, 64, 128, 224, 256) and cfg.splits >= 1
+                checked += 1
+    assert checked == 12 * 7 * 3 * 4 * 10
+
