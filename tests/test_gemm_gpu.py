@@ -577,6 +577,21 @@ def test_many_tiles_per_cta_with_odd_k_block_counts(m, n, k, sm, sn, sk, quant, 
     run_case(left, right_phys, ls, rs, quant=quant, qn=16, config=config, pow2_scales=mx)
 
 
+@pytest.mark.parametrize("quant,qn,out_t,sdt", [(False, 16, False, torch.float32), (True, 16, False, torch.float32),
+                                                (True, 32, False, torch.bfloat16), (True, 16, True, torch.float32),
+                                                (True, 128, True, torch.float32), (False, 16, True, torch.float32)])
+def test_heuristic_plan_on_256x224_pair_tiles(quant, qn, out_t, sdt):
+    """1024 x 7168: 128 CTA-pair tiles of 256 x 224 take two rounds like 112 of 256 x 256 and are narrower, so
+    the heuristic picks them (also with the operands swapped for a transposed result); all output modes."""
+    m, n, k = 1024, 7168, 512
+    left, right_phys, ls, rs = make_inputs(m, n, k, 1, 1, k, sdt, seed=92)
+    problem = _direct_problem(m, n, k, 1, 1, k, quant, qn, out_t=out_t, scale_dtype=sdt)
+    cfg = MxbConfig()
+    assert _ext.lib.mxb_default_config(ctypes.byref(problem), ctypes.byref(cfg)) == _ext.MXB_OK
+    assert cfg.cta_pair == 2 and cfg.bn == 224, cfg.key()
+    run_case(left, right_phys, ls, rs, quant=quant, qn=qn, out_t=out_t)
+
+
 def test_c_abi_direct_call_with_canaries():
     m, n, k, qn = 200, 336, 272, 16
     left, right_phys, ls, rs = make_inputs(m, n, k, 1, 1, k, seed=60)
