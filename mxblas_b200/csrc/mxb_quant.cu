@@ -44,6 +44,34 @@ __device__ __forceinline__ uint8_t quant_elem(float x, float scale) {
   q = fminf(fmaxf(q, -448.0f), 448.0f);
   return static_cast<uint8_t>(__nv_cvt_float_to_fp8(q, __NV_SATFINITE, __NV_E4M3));
 }
+// The same values without a division per element, for 16-bit inputs: with r = 1 / scale (one division per block),
+// q0 = x * r and q1 = fma(fma(-q0, scale, x), r, q0), the quotient rounded to the tensor's dtype equals
+// RN_dt(x / scale) for EVERY 16-bit x and EVERY 16-bit scale in [1e-30, 1e30] with |x| <= 1024 * scale (the
+// quantiser only divides |x| <= amax ~ 448 * scale): checked exhaustively on the GPU, 0.89 G bf16 pairs and
+// 1.55 G fp16 pairs, no difference. Outside that range of scales, and for fp32 inputs, the division stays.
+// Two elements at a time: one conversion to the 16-bit type and one to FP8 per pair.
+template <int DT>
+__device__ __forceinline__ bool reciprocal_is_exact(float scale) {
+  return DT != MXB_FP32 && scale >= 1e-30f && scale <= 1e30f;
+}
+template <int DT>
+__device__ __forceinline__ uint32_t quant_pair_recip(float x0, float x1, float scale, float r) {
+  const float p0 = x0 * r, p1 = x1 * r;
+  float q0 = fmaf(fmaf(-p0, scale, x0), r, p0), q1 = fmaf(fmaf(-p1, scale, x1), r, p1);
+  if (DT == MXB_BF16) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(q0, q1);
+    const uint32_t bits = *reinterpret_cast<const uint32_t*>(&h);
+    q0 = __uint_as_float(bits << 16);
+    q1 = __uint_as_float(bits & 0xFFFF0000u);
+  } else {
+    const __half2 h = __floats2half2_rn(q0, q1);
+    q0 = __low2float(h);
+    q1 = __high2float(h);
+  }
+  q0 = fminf(fmaxf(q0, -448.0f), 448.0f);
+  q1 = fminf(fmaxf(q1, -448.0f), 448.0f);
+  return static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(q0, q1), __NV_SATFINITE, __NV_E4M3));  // x in the low byte
+}
 
 // 16-byte vector of the input type: VEC elements
 template <int DT> struct Vec { static constexpr int N = DT == MXB_FP32 ? 4 : 8; };
@@ -72,8 +100,14 @@ __device__ __forceinline__ void load_vec(const void* x, long long i, float (&v)[
 template <int DT>
 __device__ __forceinline__ void store_codes(uint8_t* dst, const float (&v)[Vec<DT>::N], float s) {
   uint32_t w[2] = {0, 0};
+  if (reciprocal_is_exact<DT>(s)) {
+    const float r = 1.0f / s;
 #pragma unroll
-  for (int j = 0; j < Vec<DT>::N; ++j) w[j >> 2] |= static_cast<uint32_t>(quant_elem<DT>(v[j], s)) << (8 * (j & 3));
+    for (int j = 0; j < Vec<DT>::N; j += 2) w[j >> 2] |= quant_pair_recip<DT>(v[j], v[j + 1], s, r) << (8 * (j & 3));
+  } else {
+#pragma unroll
+    for (int j = 0; j < Vec<DT>::N; ++j) w[j >> 2] |= static_cast<uint32_t>(quant_elem<DT>(v[j], s)) << (8 * (j & 3));
+  }
   if (Vec<DT>::N == 8) *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
   else *reinterpret_cast<uint32_t*>(dst) = w[0];
 }
@@ -89,11 +123,20 @@ __global__ void quant_rows_vec(const void* x, long long m, long long k, long lon
   const long long total = m * vecs_per_row;
   const int lanes = bn / V;
   const long long nblk = k / bn;
-  for (long long i0 = (blockIdx.x * static_cast<long long>(blockDim.x)) + threadIdx.x; i0 - (threadIdx.x & 31) < total;
-       i0 += static_cast<long long>(gridDim.x) * blockDim.x) {
+  // (row, column vector) of a thread's element advance by a fixed step: one 64-bit division per thread, none per
+  // vector. (Two or four vectors per thread and turn, their loads issued together, measured 15-30 % slower:
+  // the kernel is not waiting on a single load.)
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long step_rows = stride / vecs_per_row, step_cv = stride - step_rows * vecs_per_row;
+  long long i0 = (blockIdx.x * static_cast<long long>(blockDim.x)) + threadIdx.x;
+  long long row0 = i0 / vecs_per_row, cv0 = i0 - row0 * vecs_per_row;
+  for (; i0 - (threadIdx.x & 31) < total; i0 += stride, row0 += step_rows, cv0 += step_cv) {
+    if (cv0 >= vecs_per_row) {
+      cv0 -= vecs_per_row;
+      ++row0;
+    }
     const bool live = i0 < total;
-    const long long i = live ? i0 : total - 1;
-    const long long row = i / vecs_per_row, cv = i - row * vecs_per_row;
+    const long long row = live ? row0 : m - 1, cv = live ? cv0 : vecs_per_row - 1;
     float v[V];
     load_vec<DT>(x, row * ldx + cv * V, v);
     float amax = 0.f;
@@ -175,8 +218,10 @@ __global__ void amax_slabs(const void* x, long long k, long long ldx, int bm, in
   float amax = 0.f;
   if (vec) {
     const int vpr = bn / V;
-    for (long long e = threadIdx.x; e < static_cast<long long>(r_hi - r_lo) * vpr; e += blockDim.x) {
-      const int r = r_lo + static_cast<int>(e / vpr), c = static_cast<int>(e % vpr) * V;
+    const int nvec = (r_hi - r_lo) * vpr;  // a slab holds ~32K elements: 32-bit indices
+    for (int e = threadIdx.x; e < nvec; e += blockDim.x) {
+      const int rr = e / vpr;
+      const int r = r_lo + rr, c = (e - rr * vpr) * V;
       float v[V];
       load_vec<DT>(x, (r0 + r) * ldx + c0 + c, v);
 #pragma unroll
@@ -211,8 +256,10 @@ __global__ void quant_slabs(const void* x, long long k, long long ldx, int bm, i
   const float s = block_scale<DT>(amax[blk]);
   if (vec) {
     const int vpr = bn / V;
-    for (long long e = threadIdx.x; e < static_cast<long long>(r_hi - r_lo) * vpr; e += blockDim.x) {
-      const int r = r_lo + static_cast<int>(e / vpr), c = static_cast<int>(e % vpr) * V;
+    const int nvec = (r_hi - r_lo) * vpr;
+    for (int e = threadIdx.x; e < nvec; e += blockDim.x) {
+      const int rr = e / vpr;
+      const int r = r_lo + rr, c = (e - rr * vpr) * V;
       float v[V];
       load_vec<DT>(x, (r0 + r) * ldx + c0 + c, v);
       store_codes<DT>(codes + (r0 + r) * ldq + c0 + c, v, s);
