@@ -48,7 +48,8 @@ __device__ __forceinline__ uint8_t quant_elem(float x, float scale) {
 // q0 = x * r and q1 = fma(fma(-q0, scale, x), r, q0), the quotient rounded to the tensor's dtype equals
 // RN_dt(x / scale) for EVERY 16-bit x and EVERY 16-bit scale in [1e-30, 1e30] with |x| <= 1024 * scale (the
 // quantiser only divides |x| <= amax ~ 448 * scale): checked exhaustively on the GPU, 0.89 G bf16 pairs and
-// 1.55 G fp16 pairs, no difference. Outside that range of scales, and for fp32 inputs, the division stays.
+// 1.55 G fp16 pairs, no difference (signs of zeros included). Outside that range of scales, and for fp32 inputs,
+// the division stays.
 // Two elements at a time: one conversion to the 16-bit type and one to FP8 per pair.
 template <int DT>
 __device__ __forceinline__ bool reciprocal_is_exact(float scale) {
@@ -57,7 +58,8 @@ __device__ __forceinline__ bool reciprocal_is_exact(float scale) {
 template <int DT>
 __device__ __forceinline__ uint32_t quant_pair_recip(float x0, float x1, float scale, float r) {
   const float p0 = x0 * r, p1 = x1 * r;
-  float q0 = fmaf(fmaf(-p0, scale, x0), r, p0), q1 = fmaf(fmaf(-p1, scale, x1), r, p1);
+  // (a zero keeps its sign: the correction step would turn -0 into +0, and FP8 has both)
+  float q0 = p0 == 0.f ? p0 : fmaf(fmaf(-p0, scale, x0), r, p0), q1 = p1 == 0.f ? p1 : fmaf(fmaf(-p1, scale, x1), r, p1);
   if (DT == MXB_BF16) {
     const __nv_bfloat162 h = __floats2bfloat162_rn(q0, q1);
     const uint32_t bits = *reinterpret_cast<const uint32_t*>(&h);
